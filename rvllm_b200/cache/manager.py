@@ -10,9 +10,9 @@ float32 tensor [slots, *shape]; a request holds one slot id for all of them, eve
 an architecture that has no such call.  A slot's records are zero when a request
 receives it (`add` clears them), so no mixer ever sees its slot's previous holder.
 
-A request's pages are given back when it ends (`free`) and, in a windowed group,
-as soon as every slot of the page lies behind the window of all future queries
-(`advance`).  Released block-table entries read -1; no kernel touches them because
+A request's pages are given back when it ends (`free`) and, in a group whose reach
+is bounded (a window, or chunks that do not see one another), as soon as every slot of
+the page lies behind what any future query can see (`advance`).  Released block-table entries read -1; no kernel touches them because
 the window bound excludes their positions.
 
 In the reference the same duties are split between `KvStorage` (per-layer K and V
@@ -151,10 +151,9 @@ class CacheManager:
                     self.states[i] = block[ci]
         for grp in self.groups:
             if allocate:
-                shape = (len(grp.calls), num_pages, page_size, grp.need.num_kv_heads,
-                         grp.need.head_dim)
-                grp.k = torch.zeros(shape, dtype=dtype, device=device)
-                grp.v = torch.zeros(shape, dtype=dtype, device=device)
+                shape = (len(grp.calls), num_pages, page_size, grp.need.num_kv_heads)
+                grp.k = torch.zeros(shape + (grp.need.head_dim,), dtype=dtype, device=device)
+                grp.v = torch.zeros(shape + (grp.need.value_dim,), dtype=dtype, device=device)
         for i, need in enumerate(needs):
             src = cache_of[i] if cache_of[i] is not None else i
             owns = cache_of[i] is None
@@ -175,7 +174,7 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Bytes of keys and values one cached token takes over all groups."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.calls) * g.need.num_kv_heads * g.need.head_dim * size
+        return sum(len(g.calls) * g.need.num_kv_heads * (g.need.head_dim + g.need.value_dim) * size
                    for g in self.groups)
 
     # ---- requests --------------------------------------------------------------------
@@ -202,9 +201,12 @@ class CacheManager:
 
     def _first_needed_page(self, grp: Group, computed: int) -> int:
         """First page a query at position >= `computed` can still read."""
-        if grp.need.window is None:
-            return 0
-        lowest_key = max(0, computed - grp.need.window + 1)
+        lowest_key = 0
+        if grp.need.window is not None:
+            lowest_key = max(0, computed - grp.need.window + 1)
+        if grp.need.chunk is not None:
+            # the chunk of the next query begins here; earlier chunks are never read again
+            lowest_key = max(lowest_key, computed // grp.need.chunk * grp.need.chunk)
         return lowest_key // self.page_size
 
     def pages_needed(self, req, total_tokens: int) -> List[int]:

@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its configuration type and its model.
 
-config.json's `architectures[0]` picks the entry, before any weight is read, as the
+config.json's `architectures[0]` (or its `architecture` string) picks the entry, before any weight is read, as the
 reference matches GGUF's `general.architecture` first (src/weights.rs:88-100,
 303-309).  An entry holds the typed configuration class and the function that turns
 a configuration into a `ModelSpec`; the generic `Model` runs every spec.
@@ -44,6 +44,8 @@ def architecture(name: str) -> Architecture:
 
 def config_from_dict(data: Dict[str, Any], where: str = "config.json"):
     archs = data.get("architectures") if isinstance(data, dict) else None
+    if isinstance(data, dict) and isinstance(data.get("architecture"), str):
+        archs = [data["architecture"]]          # some designs name their class in one string
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
         raise ConfigError(f"{where}: missing key 'architectures' (a list naming the model class)")
     return architecture(archs[0]).config_class.from_dict(data, where)

@@ -1,0 +1,65 @@
+// Activations of the dense feed-forward, element by element.
+//   xIELU with two learned numbers p, q:
+//     z > 0 :  softplus(p) z^2 + z/2
+//     z <= 0:  (1/2 + softplus(q)) (e^z - 1 - z) + z/2
+// Arithmetic in float32 whatever the storage type.  Plain reference: tests/plain_ops.py xielu.
+#include "common.cuh"
+
+__device__ __forceinline__ float rv_softplus(float a) { return a > 20.f ? a : log1pf(expf(a)); }
+
+__device__ __forceinline__ float rv_xielu(float z, float ap, float an) {
+    return z > 0.f ? ap * z * z + 0.5f * z : an * (expm1f(z) - z) + 0.5f * z;
+}
+
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ in, const float* __restrict__ act,
+                             T* __restrict__ out, size_t total) {
+    rv_pdl_launch_dependents();
+    const float ap = rv_softplus(act[0]), an = 0.5f + rv_softplus(act[1]);
+    rv_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x)
+        rv_store(out + i, rv_xielu(rv_load(in + i), ap, an));
+}
+
+// bfloat16, eight values per 16-byte access
+__global__ void xielu_bf16x8_kernel(const uint4* __restrict__ in, const float* __restrict__ act,
+                                    uint4* __restrict__ out, size_t total8) {
+    rv_pdl_launch_dependents();
+    const float ap = rv_softplus(act[0]), an = 0.5f + rv_softplus(act[1]);
+    rv_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 raw = in[i];
+        uint4 o4;
+        const __nv_bfloat162* x2 = (const __nv_bfloat162*)&raw;
+        __nv_bfloat162* o2 = (__nv_bfloat162*)&o4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 z = __bfloat1622float2(x2[k]);
+            o2[k] = __floats2bfloat162_rn(rv_xielu(z.x, ap, an), rv_xielu(z.y, ap, an));
+        }
+        out[i] = o4;
+    }
+}
+
+extern "C" int rv_xielu_act(const void* in, const float* act, void* out, int dtype, int n_rows,
+                            int width, void* stream) {
+    if (n_rows == 0) return 0;
+    if (n_rows < 0 || width <= 0) RV_FAIL("xielu: bad sizes");
+    const size_t total = (size_t)n_rows * width;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RV_DTYPE_BF16 && total % 8 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const size_t total8 = total / 8;
+        const int blocks = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
+        rv_launch(xielu_bf16x8_kernel, dim3(blocks), dim3(256), 0, s, (const uint4*)in, act,
+                  (uint4*)out, total8);
+    } else {
+        const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+        RV_DISPATCH_DTYPE(dtype, "xielu",
+                          (rv_launch(xielu_kernel<T>, dim3(blocks), dim3(256), 0, s, (const T*)in, act,
+                                     (T*)out, total)));
+    }
+    RV_CHECK_LAUNCH("xielu");
+    return 0;
+}

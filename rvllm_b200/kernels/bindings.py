@@ -604,6 +604,108 @@ class CudaOps:
                                        c_int(out.shape[0]), c_int(out.shape[1]), self._stream()),
                     "swiglu")
 
+    # ---- layer norm (alone, or with the addition into the stream) -----------------------
+
+    def add_layernorm(self, resid, delta, weight, bias, eps, out, rows=None,
+                      delta_weight=None, delta_bias=None, delta_eps=0.0):
+        """out = LN(resid + d), d = delta or LN(delta; delta_weight, delta_bias, delta_eps);
+        `resid` None: out = LN(delta).  The stream is updated unless `rows` selects rows."""
+        if resid is not None:
+            self._need(resid, "residual stream", torch.float32)
+        elif delta is None or rows is not None or delta_weight is not None:
+            raise KernelError("add_layernorm: without a stream it takes rows to normalise, all of them")
+        self._need(weight, "norm weight", torch.float32)
+        self._need(bias, "norm bias", torch.float32)
+        self._need(out, "norm output")
+        if delta is not None:
+            self._need(delta, "pending sub-layer output")
+            if resid is not None and delta.shape != resid.shape:
+                raise KernelError("add_layernorm: the stream and the pending output differ in shape")
+        if delta_weight is not None:
+            self._need(delta_weight, "norm weight of the added rows", torch.float32)
+            self._need(delta_bias, "norm bias of the added rows", torch.float32)
+        if rows is not None:
+            self._need(rows, "row list", torch.int32)
+        n, hidden = out.shape
+        if (resid if resid is not None else delta).shape[1] != hidden or weight.shape[0] != hidden \
+                or bias.shape[0] != hidden:
+            raise KernelError("add_layernorm: widths disagree")
+        self._check(self.lib.rv_add_layernorm(
+            _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else _F32,
+            _ptr(delta_weight), _ptr(delta_bias), c_float(delta_eps), _ptr(weight), _ptr(bias),
+            _ptr(out), _code(out.dtype), _ptr(rows), c_int(n), c_int(hidden), c_float(eps),
+            self._stream()), "add_layernorm")
+
+    # ---- xIELU -----------------------------------------------------------------------
+
+    def xielu(self, z, act, out):
+        self._need(z, "xielu input")
+        self._need(out, "xielu output", z.dtype)
+        self._need(act, "xielu constants", torch.float32)
+        if z.shape != out.shape or act.numel() != 2:
+            raise KernelError("xielu: shapes disagree")
+        self._check(self.lib.rv_xielu_act(_ptr(z), _ptr(act), _ptr(out), _code(out.dtype),
+                                          c_int(out.shape[0]), c_int(out.shape[1]),
+                                          self._stream()), "xielu")
+
+    # ---- minGRU scan -----------------------------------------------------------------
+
+    def mingru_scan(self, proj, bias, state, ctx, out):
+        self._need(proj, "z|x|g rows", torch.float32)
+        self._need(bias, "z|x biases", torch.float32)
+        self._need(state, "recurrent state", torch.float32)
+        self._need(out, "mingru output")
+        width = out.shape[1]
+        if proj.shape[1] != 3 * width or bias.shape[0] != 2 * width or state.shape[1] != width:
+            raise KernelError("mingru_scan: widths disagree")
+        self._check(self.lib.rv_mingru_scan(
+            _ptr(proj), _ptr(bias), _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slot), _ptr(out),
+            _code(out.dtype), c_int(ctx.n_reqs), c_int(ctx.max_q_len), c_int(width),
+            self._stream()), "mingru_scan")
+
+    # ---- partial rotation + cache write ------------------------------------------------
+
+    def rope_partial_write(self, rows, num_heads, num_kv_heads, head_dim, v_head_dim, freq,
+                           positions, slot_mapping, k_cache, v_cache):
+        self._need(rows, "q|k|v rows")
+        if k_cache is not None:
+            self._need(k_cache, "key pages", rows.dtype)
+            self._need(v_cache, "value pages", rows.dtype)
+        inv, dims = freq if freq is not None else (None, 0)
+        if inv is not None:
+            self._need(inv, "rotation frequencies", torch.float32)
+            if inv.shape[0] != dims // 2:
+                raise KernelError("rope_partial_write: one frequency per pair of turning dimensions")
+        self._check(self.lib.rv_rope_partial_write(
+            _ptr(rows), _code(rows.dtype), c_int(rows.shape[1]), c_int(rows.shape[0]),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(v_head_dim), _ptr(inv),
+            c_int(dims), _ptr(positions), _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache),
+            self._stream()), "rope_partial_write")
+
+    # ---- attention with mixed heads ------------------------------------------------------
+
+    def paged_attention_mixed(self, rows, gate_off, num_heads, num_kv_heads, head_dim, v_head_dim,
+                              k_cache, v_cache, ctx, group, scale, window, chunk, head_mix, sinks,
+                              out):
+        self._need(rows, "query rows")
+        self._need(out, "attention output", rows.dtype)
+        self._need(k_cache, "key pages", rows.dtype)
+        self._need(v_cache, "value pages", rows.dtype)
+        if head_mix is not None:
+            self._need(head_mix, "head mixing matrix", torch.float32)
+        if sinks is not None:
+            self._need(sinks, "sinks", torch.float32)
+        if out.shape[1] != num_heads * v_head_dim:
+            raise KernelError("paged_attention_mixed: output width and head sizes disagree")
+        self._check(self.lib.rv_paged_attention_mixed(
+            _ptr(rows), _code(rows.dtype), c_int(rows.shape[1]), c_int(gate_off), _ptr(k_cache),
+            _ptr(v_cache), _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
+            _ptr(ctx.ctx_lens), _ptr(ctx.token_req), _ptr(out), c_int(0), c_int(ctx.n_tokens),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(v_head_dim),
+            c_int(group.page_size), c_float(scale), c_int(window if window else 0),
+            c_int(chunk if chunk else 0), _ptr(head_mix), _ptr(sinks), self._stream()),
+            "paged_attention_mixed")
+
     # ---- sampling --------------------------------------------------------------------
 
     def argmax(self, logits):

@@ -25,10 +25,24 @@ from .spec import ParamDecl
 
 @dataclass(frozen=True)
 class PagedNeed:
-    """Keys and values of every token (or of the last `window` tokens), in pages."""
+    """Keys and values of every token, in pages.  `window`: only the last `window` positions
+    are ever read again; `chunk`: only the positions of the newest chunk of `chunk` positions
+    (counted from position 0) are.  Both tell the cache manager which pages it may take
+    back early; neither changes the layout.  `v_head_dim`: size of a value head when it is
+    not the key size."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim if self.v_head_dim else self.head_dim
+
+    def layout(self):
+        """What two calls must agree on to share pages."""
+        return (self.num_kv_heads, self.head_dim, self.value_dim)
 
 
 @dataclass(frozen=True)
@@ -85,9 +99,12 @@ class FeedForward:
 
 
 class Norm:
-    """norm.add_norm(resid, delta, ctx, rows=None) adds `delta` (or nothing) to the
-    float32 residual stream in place and returns the normalised rows in the compute
-    dtype; with `rows` it reads only those rows and leaves the stream untouched.
+    """norm.add_norm(resid, delta, ctx, rows=None, delta_norm=None) adds `delta` (or
+    nothing) to the float32 residual stream in place and returns the normalised rows in the
+    compute dtype; with `rows` it reads only those rows and leaves the stream untouched.
+    `delta_norm` is a norm that `delta` still has to pass through before it is added (a norm
+    placed after a sub-layer): a class that can do both in one kernel does, any other calls
+    `delta_norm.norm` first (`_normed_delta`).
     norm.norm(x, ctx) normalises rows that are not part of the stream."""
 
     @staticmethod
@@ -97,8 +114,14 @@ class Norm:
     def __init__(self, spec, tensors, ops, dtype):
         raise NotImplementedError
 
-    def add_norm(self, resid, delta, ctx, rows=None):
+    def add_norm(self, resid, delta, ctx, rows=None, delta_norm=None):
         raise NotImplementedError
+
+    @staticmethod
+    def _normed_delta(delta, delta_norm, ctx):
+        if delta is None or delta_norm is None:
+            return delta
+        return delta_norm.norm(delta, ctx)
 
     def norm(self, x, ctx):
         """The normalised rows of `x` (compute dtype), with no residual stream involved:
@@ -143,7 +166,8 @@ class Arrangement:
 @dataclass
 class Stream:
     resid: object                   # float32 [N, hidden]
-    pending: Optional[object]       # compute dtype [N, hidden], not yet added
+    pending: Optional[object]       # [N, hidden], not yet added
+    pending_norm: Optional[object] = None   # a Norm `pending` has to pass through first
 
 
 _MIXERS: Dict[str, type] = {}

@@ -4,7 +4,8 @@
 `Layer::forward`, src/model.rs:556-585), with the reference's optional norms of the
 mixer's and the feed-forward's output before each addition (src/model.rs:571, 581;
 LFM2 uses neither).  The residual stream is float32; each sub-layer's output stays pending and is
-added by the next norm's kernel.
+added by the next norm's kernel, together with the norm it still has to pass through when
+the block has one after the sub-layer.  A block without a feed-forward is its first half.
 """
 from __future__ import annotations
 
@@ -17,6 +18,28 @@ def _sub(tensors, prefix):
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
+def norm_tensor_names(norm, name):
+    """{local name: name in the file} of a norm whose place was given `name`: one name is
+    the weight's; a mapping is taken as it is."""
+    if isinstance(name, str):
+        return {"weight": name}
+    return dict(name)
+
+
+def norm_params(norm, name):
+    decls = norm_class(norm.kind).params(norm)
+    names = norm_tensor_names(norm, name)
+    if set(names) != set(decls):
+        raise ValueError(f"a {norm.kind} norm has tensors {sorted(decls)}, "
+                         f"but names were given for {sorted(names)}")
+    return {names[k]: d for k, d in decls.items()}
+
+
+def build_norm(norm, name, tensors, ops, dtype):
+    names = norm_tensor_names(norm, name)
+    return norm_class(norm.kind)(norm, {k: tensors[n] for k, n in names.items()}, ops, dtype)
+
+
 class PreNormBlock(Arrangement):
     REQUIRED = ("mixer", "ffn")
     OPTIONAL = ("post_mixer", "post_ffn")
@@ -25,9 +48,13 @@ class PreNormBlock(Arrangement):
     def _check(spec: BlockSpec):
         places = PreNormBlock.REQUIRED + PreNormBlock.OPTIONAL
         for place in PreNormBlock.REQUIRED:
+            if place == "ffn" and spec.feed_forward is None:
+                continue
             if place not in spec.norms:
                 raise ValueError(f"a pre_norm block needs a norm at {place!r}")
         for place in spec.norms:
+            if spec.feed_forward is None and place in ("ffn", "post_ffn"):
+                raise ValueError(f"a block without a feed-forward has no place {place!r}")
             if place not in places:
                 raise ValueError(f"a pre_norm block has no place {place!r} for a norm "
                                  f"(places: {', '.join(places)})")
@@ -41,10 +68,12 @@ class PreNormBlock(Arrangement):
         mixer_params = mixer.params(spec.mixer, owns_cache)
         for k, d in mixer_params.items():
             out[spec.mixer_prefix + k] = d
-        for k, d in feed_forward_class(spec.feed_forward.kind).params(spec.feed_forward).items():
-            out[spec.ffn_prefix + k] = d
+        if spec.feed_forward is not None:
+            ff = feed_forward_class(spec.feed_forward.kind).params(spec.feed_forward)
+            for k, d in ff.items():
+                out[spec.ffn_prefix + k] = d
         for norm, name in spec.norms.values():
-            out[name] = norm_class(norm.kind).params(norm)["weight"]
+            out.update(norm_params(norm, name))
         return out
 
     def __init__(self, spec: BlockSpec, tensors, ops, dtype):
@@ -52,28 +81,28 @@ class PreNormBlock(Arrangement):
         self.spec = spec
         self.mixer = mixer_class(spec.mixer.kind)(
             spec.mixer, _sub(tensors, spec.mixer_prefix), ops, dtype)
-        self.feed_forward = feed_forward_class(spec.feed_forward.kind)(
-            spec.feed_forward, _sub(tensors, spec.ffn_prefix), ops, dtype)
+        self.feed_forward = None if spec.feed_forward is None else \
+            feed_forward_class(spec.feed_forward.kind)(
+                spec.feed_forward, _sub(tensors, spec.ffn_prefix), ops, dtype)
 
         def build(place):
             if place not in spec.norms:
                 return None
             norm, name = spec.norms[place]
-            return norm_class(norm.kind)(norm, {"weight": tensors[name]}, ops, dtype)
+            return build_norm(norm, name, tensors, ops, dtype)
 
         self.mixer_norm, self.ffn_norm = build("mixer"), build("ffn")
         self.post_mixer, self.post_ffn = build("post_mixer"), build("post_ffn")
 
     def forward(self, stream: Stream, ctx, cache) -> Stream:
-        normed = self.mixer_norm.add_norm(stream.resid, stream.pending, ctx)
+        normed = self.mixer_norm.add_norm(stream.resid, stream.pending, ctx,
+                                          delta_norm=stream.pending_norm)
         mixed = self.mixer.forward(normed, ctx, cache)
-        if self.post_mixer is not None:
-            mixed = self.post_mixer.norm(mixed, ctx)
-        normed2 = self.ffn_norm.add_norm(stream.resid, mixed, ctx)
+        if self.feed_forward is None:
+            return Stream(stream.resid, mixed, self.post_mixer)
+        normed2 = self.ffn_norm.add_norm(stream.resid, mixed, ctx, delta_norm=self.post_mixer)
         out = self.feed_forward.forward(normed2, ctx)
-        if self.post_ffn is not None:
-            out = self.post_ffn.norm(out, ctx)
-        return Stream(stream.resid, out)
+        return Stream(stream.resid, out, self.post_ffn)
 
 
 register_arrangement("pre_norm", PreNormBlock)

@@ -11,7 +11,10 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .base import Stream, arrangement_class, mixer_class, norm_class
+import dataclasses
+
+from .base import PagedNeed, Stream, arrangement_class, mixer_class, norm_class
+from .block import build_norm, norm_params
 from .spec import ModelSpec, ParamDecl
 
 
@@ -28,8 +31,8 @@ def param_decls(spec: ModelSpec) -> Dict[str, ParamDecl]:
     """Every tensor the model reads, by its name in the file."""
     out: Dict[str, ParamDecl] = {
         spec.embedding_name: ParamDecl((spec.vocab_size, spec.hidden), "embedding"),
-        spec.final_norm_name: norm_class(spec.final_norm.kind).params(spec.final_norm)["weight"],
     }
+    out.update(norm_params(spec.final_norm, spec.final_norm_name))
     if spec.head_name is not None:
         out[spec.head_name] = ParamDecl((spec.vocab_size, spec.hidden), "linear")
     used = {call.layer for call in spec.order}
@@ -56,7 +59,10 @@ def validate_order(spec: ModelSpec) -> None:
                 spec.layers[call.layer].mixer)
             b = mixer_class(spec.layers[src.layer].mixer.kind).cache_need(
                 spec.layers[src.layer].mixer)
-            if a != b:
+            same = a == b
+            if isinstance(a, PagedNeed) and isinstance(b, PagedNeed):
+                same = a.layout() == b.layout()       # their reach may differ: see cache_needs
+            if not same:
                 raise ValueError(f"run order entry {pos} reads the cache of entry "
                                  f"{call.cache_of}, whose cache has another shape")
 
@@ -70,20 +76,28 @@ class Model:
         self.embedding = tensors[spec.embedding_name].contiguous()
         self.head = (tensors[spec.head_name].contiguous() if spec.head_name is not None
                      else self.embedding)
-        self.final_norm = norm_class(spec.final_norm.kind)(
-            spec.final_norm, {"weight": tensors[spec.final_norm_name]}, ops, dtype)
+        self.final_norm = build_norm(spec.final_norm, spec.final_norm_name, tensors, ops, dtype)
         used = {call.layer for call in spec.order}
         self.blocks = [arrangement_class(b.arrangement)(b, tensors, ops, dtype)
                        if i in used else None for i, b in enumerate(spec.layers)]
         self.device = self.embedding.device
 
     def cache_needs(self) -> List[Optional[object]]:
-        """What each call of the run order has to remember (None: nothing of its own)."""
+        """What each call of the run order has to remember (None: nothing of its own).
+        A call that reads another call's pages may look further back than their owner (another
+        window or chunk): the owner's pages are then kept for as long as the request lives."""
         needs = []
         for call in self.spec.order:
             m = self.spec.layers[call.layer].mixer
-            needs.append(None if call.cache_of is not None
-                         else mixer_class(m.kind).cache_need(m))
+            need = mixer_class(m.kind).cache_need(m)
+            if call.cache_of is None:
+                needs.append(need)
+                continue
+            needs.append(None)
+            own = needs[call.cache_of]
+            if isinstance(own, PagedNeed) and isinstance(need, PagedNeed) and \
+                    (own.window, own.chunk) != (need.window, need.chunk):
+                needs[call.cache_of] = dataclasses.replace(own, window=None, chunk=None)
         return needs
 
     def forward(self, ctx, caches) -> torch.Tensor:
@@ -98,5 +112,5 @@ class Model:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32,
                                device=self.device)
         normed = self.final_norm.add_norm(stream.resid, stream.pending, ctx,
-                                          rows=ctx.logit_rows)
+                                          rows=ctx.logit_rows, delta_norm=stream.pending_norm)
         return self.ops.linear(normed, self.head, out_dtype=torch.float32)

@@ -27,7 +27,8 @@ class RMSNorm(Norm):
         # bfloat16 file without loss.
         self.weight = tensors["weight"].to(torch.float32).contiguous()
 
-    def add_norm(self, resid, delta, ctx, rows=None):
+    def add_norm(self, resid, delta, ctx, rows=None, delta_norm=None):
+        delta = self._normed_delta(delta, delta_norm, ctx)
         n = resid.shape[0] if rows is None else rows.shape[0]
         out = self.ops.new_rows(n, self.spec.size, self.dtype, resid.device)
         self.ops.add_rmsnorm(resid, delta, self.weight, self.spec.eps, out, rows)
@@ -40,4 +41,44 @@ class RMSNorm(Norm):
         return out
 
 
+class LayerNorm(Norm):
+    """(x - mean) / sqrt(var + eps) * weight + bias, var the mean squared deviation;
+    statistics, the normalised values and the sum with the residual stream in float32.
+
+    `norm(x)` (a norm after a sub-layer) gives float32 rows, because they are on their way
+    into the float32 stream; when the next norm of the stream is a LayerNorm too, the two
+    and the addition between them are one kernel: x = stream + LN_a(delta); out = LN_b(x).
+    """
+
+    @staticmethod
+    def params(spec: NormSpec):
+        return {"weight": ParamDecl((spec.size,), "norm"),
+                "bias": ParamDecl((spec.size,), "bias")}
+
+    def __init__(self, spec: NormSpec, tensors, ops, dtype):
+        self.spec = spec
+        self.ops = ops
+        self.dtype = dtype
+        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.bias = tensors["bias"].to(torch.float32).contiguous()
+
+    def add_norm(self, resid, delta, ctx, rows=None, delta_norm=None):
+        n = resid.shape[0] if rows is None else rows.shape[0]
+        out = self.ops.new_rows(n, self.spec.size, self.dtype, resid.device)
+        if delta is not None and isinstance(delta_norm, LayerNorm):
+            self.ops.add_layernorm(resid, delta, self.weight, self.bias, self.spec.eps, out, rows,
+                                   delta_weight=delta_norm.weight, delta_bias=delta_norm.bias,
+                                   delta_eps=delta_norm.spec.eps)
+            return out
+        delta = self._normed_delta(delta, delta_norm, ctx)
+        self.ops.add_layernorm(resid, delta, self.weight, self.bias, self.spec.eps, out, rows)
+        return out
+
+    def norm(self, x, ctx):
+        out = torch.empty((x.shape[0], self.spec.size), dtype=torch.float32, device=x.device)
+        self.ops.add_layernorm(None, x, self.weight, self.bias, self.spec.eps, out, None)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

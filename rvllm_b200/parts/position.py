@@ -38,6 +38,31 @@ class Rope(PositionEncoding):
         return self.cos, self.sin
 
 
+class PartialRope(PositionEncoding):
+    """The rotate-half rotation on the first `rot_dims` dimensions of a head only: dimension
+    i turns with i + rot_dims/2 by the angle pos * theta^(-2i/rot_dims); the others pass.
+    There is no table over positions: the kernels form the angle (float32) from the position
+    and `frequencies()`, so no longest context has to be known."""
+
+    def __init__(self, spec: PositionSpec, device):
+        dims = spec.rot_dims or spec.head_dim
+        if dims % 2 or dims > spec.head_dim or dims < 0:
+            raise ValueError(f"rope_partial needs an even number of turning dimensions within "
+                             f"the head's {spec.head_dim}, got {dims}")
+        self.spec = spec
+        self.rot_dims = dims
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        self.inv_freq = torch.pow(torch.tensor(spec.theta, dtype=torch.float64),
+                                  -2.0 * i / max(dims, 1)).to(torch.float32).to(device).contiguous()
+
+    def rotation_table(self):
+        return None
+
+    def frequencies(self):
+        """(float32 [rot_dims/2] angle per position of each pair, rot_dims)"""
+        return self.inv_freq, self.rot_dims
+
+
 class NoPosition(PositionEncoding):
     def __init__(self, spec: PositionSpec, device):
         self.spec = spec
@@ -47,4 +72,5 @@ class NoPosition(PositionEncoding):
 
 
 register_position("rope", Rope)
+register_position("rope_partial", PartialRope)
 register_position("none", NoPosition)

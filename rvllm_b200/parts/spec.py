@@ -47,11 +47,13 @@ class NormSpec:
 
 @dataclass(frozen=True)
 class PositionSpec:
-    """How positions enter the attention mixer. kind "none" applies nothing."""
+    """How positions enter the attention mixer. kind "none" applies nothing.
+    `rot_dims` (kind "rope_partial"): only the first rot_dims dimensions of a head turn."""
     kind: str
     head_dim: int = 0
     theta: float = 0.0
     max_position: int = 0
+    rot_dims: int = 0
 
 
 @dataclass(frozen=True)
@@ -70,6 +72,35 @@ class AttentionSpec(MixerSpec):
     window: Optional[int] = None                # keys visible: the last `window` positions
     scale: Optional[float] = None               # None: 1/sqrt(head_dim)
     # local tensor name -> suffix in the file
+    names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+
+
+@dataclass(frozen=True)
+class MixedAttentionSpec(AttentionSpec):
+    """Attention whose heads are not independent of one another, with a few more options;
+    each is off at its default.
+
+    v_head_dim  size of a value head (0: the key size)
+    chunk       a query sees only the keys of its own chunk of `chunk` positions, counted
+                from position 0 of the sequence (None: no such bound)
+    head_mix    scores are mixed over the heads before the softmax: s'_h = sum_g M[h, g] s_g
+                (tensor "talk" [heads, heads])
+    sinks       the softmax's denominator has one more term exp(sink_h) with no key or value
+                (tensor "sink" [heads])
+    out_gate    the concatenated heads are multiplied by sigmoid(gate(x)) before the output
+                product (tensor "g" [heads * v_head_dim, hidden])
+    """
+    v_head_dim: int = 0
+    chunk: Optional[int] = None
+    head_mix: bool = False
+    sinks: bool = False
+    out_gate: bool = False
+
+
+@dataclass(frozen=True)
+class MinGRUSpec(MixerSpec):
+    """A gated recurrence whose gates read only the current token; `width` channels."""
+    width: int = 0
     names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
 
 
@@ -93,11 +124,21 @@ class SwiGLUSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class DenseSpec(FeedForwardSpec):
+    """down(act(up(x))) with one of the registered activations."""
+    ffn_dim: int = 0
+    activation: str = "xielu"
+    names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: which parts and how they are arranged.
 
-    `norms` maps a place in the block to (norm spec, tensor name in the file); which
-    places exist is the arrangement's business.  "pre_norm" (src/model.rs:556-585):
+    `norms` maps a place in the block to (norm spec, tensor name in the file); a norm with
+    more than one tensor gives a mapping {local name: name in the file} instead of the one
+    name.  Which places exist is the arrangement's business.  `feed_forward` None: the block
+    is its mixer alone.  "pre_norm" (src/model.rs:556-585):
         h = x + post_mixer(mixer(mixer_norm(x)));  out = h + post_ffn(ffn(ffn_norm(h)))
     with places "mixer" and "ffn" required and "post_mixer", "post_ffn" optional (the
     reference's `post_attn_norm` and `post_ffn_norm`, src/model.rs:571, 581; LFM2 has
@@ -106,8 +147,8 @@ class BlockSpec:
     """
     arrangement: str
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
-    norms: Mapping[str, Tuple[NormSpec, str]] = field(hash=False)
+    feed_forward: Optional[FeedForwardSpec]
+    norms: Mapping[str, Tuple[NormSpec, object]] = field(hash=False)
     mixer_prefix: str = ""
     ffn_prefix: str = ""
 
@@ -131,7 +172,7 @@ class ModelSpec:
     order: Tuple[LayerCall, ...]
     final_norm: NormSpec
     embedding_name: str
-    final_norm_name: str
+    final_norm_name: object                     # a name, or {local name: name in the file}
     head_name: Optional[str]                    # None: the head is the embedding table
     embedding_scale: Optional[float] = None
     bos_token_id: Optional[int] = None

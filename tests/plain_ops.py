@@ -158,6 +158,121 @@ class PlainOps:
         g, u = _f(gate_up[:, :f]), _f(gate_up[:, f:])
         out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
+    # ---- layer norm, alone or with the addition into the stream ------------------------
+    def add_layernorm(self, resid, delta, weight, bias, eps, out, rows=None,
+                      delta_weight=None, delta_bias=None, delta_eps=0.0):
+        def ln(x, w, b, e):
+            mu = x.mean(dim=-1, keepdim=True)
+            var = (x - mu).pow(2).mean(dim=-1, keepdim=True)
+            return (x - mu) / (var + e).sqrt() * _f(w) + _f(b)
+
+        d = None if delta is None else _f(delta)
+        if d is not None and delta_weight is not None:
+            d = ln(d, delta_weight, delta_bias, delta_eps)
+        if resid is None:
+            x = d
+        elif rows is None:
+            if d is not None:
+                resid.add_(d)
+            x = resid
+        else:
+            x = resid[rows.long()]
+            if d is not None:
+                x = x + d[rows.long()]
+        out.copy_(ln(x, weight, bias, eps).to(out.dtype))
+
+    # ---- xIELU -----------------------------------------------------------------------
+    def xielu(self, z, act, out):
+        x = _f(z)
+        sp = lambda a: torch.log1p(torch.exp(_f(a)))
+        pos = sp(act[0]) * x * x + 0.5 * x
+        neg = (0.5 + sp(act[1])) * (torch.expm1(torch.clamp(x, max=0.0)) - x) + 0.5 * x
+        out.copy_(torch.where(x > 0, pos, neg).to(out.dtype))
+
+    # ---- minGRU scan -----------------------------------------------------------------
+    def mingru_scan(self, proj, bias, state, ctx, out):
+        w = out.shape[1]
+        q_start = ctx.q_start.tolist()
+        slots = ctx.state_slot.tolist()
+        p = _f(proj)
+        for r in range(ctx.n_reqs):
+            a, b = q_start[r], q_start[r + 1]
+            if slots[r] < 0 or a == b:
+                continue
+            s = state[slots[r]].clone()
+            for t in range(a, b):
+                z = torch.sigmoid(p[t, :w] + _f(bias[:w]))
+                u = p[t, w:2 * w] + _f(bias[w:])
+                c = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+                s = (1 - z) * s + z * c
+                g = p[t, 2 * w:]
+                out[t] = (s * g * torch.sigmoid(g)).to(out.dtype)
+            state[slots[r]] = s
+
+    # ---- partial rotation + cache write ------------------------------------------------
+    def rope_partial_write(self, rows, num_heads, num_kv_heads, head_dim, v_head_dim, freq,
+                           positions, slot_mapping, k_cache, v_cache):
+        n = rows.shape[0]
+        H, G, d, dv = num_heads, num_kv_heads, head_dim, v_head_dim
+
+        def turn(x):                       # [n, heads, d] float32
+            if freq is None:
+                return x
+            inv, dims = freq
+            half = dims // 2
+            a = positions.to(torch.float32)[:, None] * inv[None, :]
+            cos, sin = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
+            u, v = x[..., :half], x[..., half:dims]
+            return torch.cat([u * cos - v * sin, v * cos + u * sin, x[..., dims:]], dim=-1)
+
+        q = turn(_f(rows[:, :H * d]).reshape(n, H, d))
+        rows[:, :H * d] = q.reshape(n, H * d).to(rows.dtype)
+        if G:
+            k = turn(_f(rows[:, H * d:(H + G) * d]).reshape(n, G, d))
+            v = rows[:, (H + G) * d:(H + G) * d + G * dv].reshape(n, G, dv)
+            kc, vc = k_cache.view(-1, G, d), v_cache.view(-1, G, dv)
+            for t in range(n):
+                s = int(slot_mapping[t])
+                if s >= 0:
+                    kc[s] = k[t].to(kc.dtype)
+                    vc[s] = v[t].to(vc.dtype)
+
+    # ---- attention with mixed heads over the pages ---------------------------------------
+    def paged_attention_mixed(self, rows, gate_off, num_heads, num_kv_heads, head_dim, v_head_dim,
+                              k_cache, v_cache, ctx, group, scale, window, chunk, head_mix, sinks,
+                              out):
+        H, G, d, dv = num_heads, num_kv_heads, head_dim, v_head_dim
+        kv_of = torch.arange(H) // (H // G)
+        ps = group.page_size
+        q_start = ctx.q_start.tolist()
+        ctx_lens = ctx.ctx_lens.tolist()
+        for r in range(ctx.n_reqs):
+            clen = ctx_lens[r]
+            a, b = q_start[r], q_start[r + 1]
+            if clen == 0:
+                out[a:b] = 0
+                continue
+            table = group.block_table[r].tolist()
+            for t in range(a, b):
+                p = clen - (b - a) + (t - a)
+                lo = 0 if window is None else max(0, p - window + 1)
+                if chunk:
+                    lo = max(lo, p // chunk * chunk)
+                idx = torch.tensor([table[j // ps] * ps + j % ps for j in range(lo, p + 1)])
+                k = _f(k_cache.view(-1, G, d)[idx])[:, kv_of]          # [keys, H, d]
+                v = _f(v_cache.view(-1, G, dv)[idx])[:, kv_of]
+                q = _f(rows[t, :H * d]).reshape(H, d)
+                s = torch.einsum("hd,jhd->hj", q, k) * scale
+                if head_mix is not None:
+                    s = _f(head_mix) @ s
+                if sinks is not None:
+                    s = torch.cat([s, _f(sinks)[:, None]], dim=1)
+                w = torch.softmax(s, dim=1)[:, :idx.shape[0]]
+                o = torch.einsum("hj,jhd->hd", w, v).reshape(H * dv)
+                if gate_off >= 0:
+                    o = o * torch.sigmoid(_f(rows[t, gate_off:gate_off + H * dv]))
+                out[t] = o.to(out.dtype)
+
     # ---- sampling --------------------------------------------------------------------
     def argmax(self, logits):
         out = torch.zeros(logits.shape[0], dtype=torch.int32)
