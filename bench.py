@@ -33,6 +33,10 @@ steps it holds 4096 - K tokens, then K steps are timed with CUDA events and end 
              events recorded around it (`gpu_idle_frac`: the share of the run's wall time in
              which the device waited for the host)
 
+`--only retorax` (not part of the default run) measures another design, Retorax, beside LFM2
+at equal sizes (width 1024 and 2048, eight layers): a 2,048-token prompt, single tokens at
+batch 8 and 64, and the device time of every kernel of a step against its roofline.
+
 RVLLM_BENCH_PAGE sets the tokens per cache page (16; 64 measured the same).
 
 Peaks come from MEASURED_PEAKS.json beside this file when it exists ("of measured"),
@@ -811,6 +815,231 @@ def run_further(args):
     return 0
 
 
+# ---- another design beside LFM2 ---------------------------------------------------------------
+
+RETORAX_SIZES = {
+    # width, layers (recurrence and attention in turn; every second attention reads the keys
+    # and values of the one before it), heads / kv heads, key = value size, chunk, ff, vocab
+    "w1024": {"width": 1024, "layers": 8, "heads": 16, "kv": 4, "dim": 64, "chunk": 1024,
+              "ff": 4096, "vocab": 32768},
+    "w2048": {"width": 2048, "layers": 8, "heads": 32, "kv": 8, "dim": 64, "chunk": 2048,
+              "ff": 8192, "vocab": 32768},
+}
+FP32_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12      # CUDA-core FMA rate at the top clock
+
+
+def retorax_config(sz):
+    layers, last_kv = [], None
+    for i in range(sz["layers"]):
+        mlp = {"kind": "dense", "ff": sz["ff"]}
+        if i % 2 == 0:
+            layers.append({"type": "mingru", "mixer": {"width": sz["width"]}, "mlp": mlp})
+            continue
+        mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"],
+                 "scale": sz["dim"] ** -0.5, "rot": {"dims": sz["dim"] // 2, "base": 10000.0},
+                 "mask": {"size": sz["chunk"]}}
+        if last_kv is not None and (i // 2) % 2 == 1:
+            mixer["kv_from"] = last_kv
+        else:
+            last_kv = i
+        layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Retorax", "vocab": sz["vocab"], "width": sz["width"],
+            "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def lfm2_like(sz):
+    """LFM2 with the same width, layer count, attention places and head sizes, and a SwiGLU of
+    as many parameters as the dense feed-forward (three matrices of 2/3 the inner width)."""
+    d = dict(LFM2_1_2B)
+    d.update(num_hidden_layers=sz["layers"], full_attn_idxs=list(range(1, sz["layers"], 2)),
+             hidden_size=sz["width"], num_attention_heads=sz["heads"],
+             num_key_value_heads=sz["kv"], head_dim=sz["dim"], block_ff_dim=sz["ff"],
+             block_auto_adjust_ff_dim=True, block_multiple_of=256, vocab_size=sz["vocab"],
+             max_position_embeddings=8192)
+    return d
+
+
+class OpTimer:
+    """Device time of each call of the kernel set's methods, by CUDA events around the call."""
+    NAMES = ("embed", "add_rmsnorm", "add_layernorm", "linear", "linear_qk_norm_rope_write",
+             "rope_partial_write", "paged_attention", "paged_attention_mixed", "short_conv",
+             "mingru_scan", "swiglu", "xielu")
+
+    def __init__(self, torch, ops):
+        self.torch, self.ops, self.events, self.saved = torch, ops, [], {}
+
+    def __enter__(self):
+        for name in self.NAMES:
+            fn = getattr(self.ops, name)
+            self.saved[name] = fn
+
+            def wrapped(*a, _fn=fn, _name=name, **kw):
+                e0 = self.torch.cuda.Event(enable_timing=True)
+                e1 = self.torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = _fn(*a, **kw)
+                e1.record()
+                self.events.append((_name, e0, e1))
+                return out
+            setattr(self.ops, name, wrapped)
+        return self
+
+    def __exit__(self, *exc):
+        for name in self.saved:
+            delattr(self.ops, name)           # the class's method shows again
+        return False
+
+    def totals(self):
+        self.torch.cuda.synchronize()
+        out = {}
+        for name, e0, e1 in self.events:
+            t = out.setdefault(name, [0, 0.0])
+            t[0] += 1
+            t[1] += e0.elapsed_time(e1) * 1e3
+        return {k: {"calls": v[0], "us": round(v[1], 1)} for k, v in out.items()}
+
+
+def run_designs(args):
+    """Retorax beside LFM2 at equal sizes (`--only retorax`): prompt and single-token
+    throughput, and the device time of every kernel of one prompt step and one single-token
+    step with its share of the roofline.  One JSON line."""
+    import torch
+
+    from rvllm_b200.config import config_from_dict
+    from rvllm_b200.engine import ModelRunner, StepEntry, graphs_default, load_model, make_cache
+    from rvllm_b200.weights import write_random_model
+
+    pk = peaks()
+    out = {"only": "retorax", "peaks": pk["source"], "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1)}
+    gen = torch.Generator().manual_seed(0)
+    T, CTX = 2048, 1024
+    for size_name, sz in RETORAX_SIZES.items():
+        if args.design_size not in ("all", size_name):
+            continue
+        entry = {}
+        for design, data in (("retorax", retorax_config(sz)), ("lfm2", lfm2_like(sz))):
+            cfg = config_from_dict(data)
+            tmp = tempfile.mkdtemp(prefix="rvllm_bench_")
+            try:
+                folder = write_random_model(os.path.join(tmp, "m"), cfg, seed=0)
+                model, cfg = load_model(folder, "bfloat16", "cuda")
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            ops = model.ops
+            vocab = model.spec.vocab_size
+            res = {"weights_MB": round(sum(t.numel() * t.element_size() for t in
+                                           [model.embedding] + [w for b in model.blocks for w in _block_tensors(b)]) / 1e6, 1)}
+
+            def ids(n):
+                return torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+            # a prompt of T tokens in one step
+            cache = make_cache(model, PAGE, T // PAGE + 1, 1)
+            runner = ModelRunner(model, cache, ops, use_graphs=False)
+            toks = ids(T)
+            times = []
+            for it in range(5):
+                runner.add_request("p")
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                runner.step([StepEntry("p", toks, (T - 1,))])
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+                runner.end_request("p")
+            ms = sorted(times[2:])[1]
+            res["prefill_2048"] = {"tok_s": round(T / (ms / 1e3), 1), "ms": round(ms, 3)}
+            runner.add_request("p")
+            with OpTimer(torch, ops) as timer:
+                runner.step([StepEntry("p", toks, (T - 1,))])
+            res["prefill_2048_kernels_us"] = timer.totals()
+            runner.end_request("p")
+            del runner, cache
+            # single tokens at batch 8 and 64, contexts around CTX
+            for b in (8, 64):
+                steps, warm = 128, 8
+                cache = make_cache(model, PAGE, b * ((CTX + steps + warm) // PAGE + 2), b)
+                runner = ModelRunner(model, cache, ops, use_graphs=graphs_default())
+                for i in range(b):
+                    runner.add_request(i)
+                    runner.step([StepEntry(i, ids(CTX - steps // 2), ())])
+                reqs = list(range(b))
+                first = runner.decode_greedy(reqs, [1] * b, warm)[-1].tolist()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                runner.decode_greedy(reqs, first, steps)
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / steps
+                res[f"decode_b{b}"] = {"tok_s": round(b / (ms / 1e3), 1), "ms_per_step": round(ms, 4)}
+                if b == 64:
+                    plain = ModelRunner(model, cache, ops, use_graphs=False)
+                    plain.step([StepEntry(i, (1,), ()) for i in reqs])          # shapes met once
+                    with OpTimer(torch, ops) as timer:
+                        plain.step([StepEntry(i, (1,), ()) for i in reqs])
+                    res["decode_b64_kernels_us"] = timer.totals()
+                    del plain
+                del runner, cache
+            ops.check_status()
+            entry[design] = res
+            del model
+            torch.cuda.empty_cache()
+        entry["rooflines"] = design_rooflines(sz, entry, pk, T, CTX)
+        out[size_name] = entry
+    print(json.dumps(out))
+    return 0
+
+
+def _block_tensors(block):
+    for part in (block.mixer, block.feed_forward):
+        for v in vars(part).values() if part is not None else ():
+            if hasattr(v, "element_size") and v.dim() == 2:
+                yield v
+
+
+def design_rooflines(sz, entry, pk, T, CTX):
+    """Per kernel pair (the new design's kernel, LFM2's like kernel): device time of all calls in
+    the prompt step, and the time the roofline allows (bytes / measured copy rate; for attention
+    tensor FLOPs / measured GEMM rate, plus, for the mixed heads, 2 H^2 float32 FLOPs a score on
+    the CUDA cores at their nominal rate)."""
+    W, F, H, G, D = sz["width"], sz["ff"], sz["heads"], sz["kv"], sz["dim"]
+    L = sz["layers"]
+    hbm = pk["hbm_gbs"] * 1e3                       # bytes per microsecond
+    tens = pk["bf16_tflops"] * 1e6                  # FLOPs per microsecond
+    fp32 = FP32_TFLOPS_NOMINAL * 1e6
+    n_attn = L // 2
+    f_lfm = -(-int(2 * F / 3) // 256) * 256
+    chunk = sz["chunk"]
+    pairs = sum(min(p % chunk, p) + 1 for p in range(T))          # (query, key) pairs of a prompt
+    pairs_full = T * (T + 1) // 2
+    ideal = {
+        # per call: stream read and written, the added rows read, the normalised rows written
+        "add_layernorm": (2 * L + 1) * T * W * (4 + 4 + 2 + 2) / hbm,
+        "add_rmsnorm": (2 * L + 1) * T * W * (4 + 4 + 2 + 2) / hbm,
+        "xielu": L * T * F * 4 / hbm,
+        "swiglu": L * T * f_lfm * 6 / hbm,
+        "mingru_scan": (L // 2) * T * W * (12 + 2) / hbm,
+        "short_conv": (L // 2) * T * W * (6 + 2) / hbm,
+        "paged_attention_mixed": n_attn * (pairs * 4.0 * H * D / tens + pairs * 2.0 * H * H / fp32),
+        "paged_attention": n_attn * pairs_full * 4.0 * H * D / tens,
+    }
+    rows = {}
+    like = (("add_layernorm", "add_rmsnorm"), ("xielu", "swiglu"), ("mingru_scan", "short_conv"),
+            ("paged_attention_mixed", "paged_attention"))
+    for ours, theirs in like:
+        a = entry["retorax"]["prefill_2048_kernels_us"].get(ours)
+        b = entry["lfm2"]["prefill_2048_kernels_us"].get(theirs)
+        if a and b:
+            rows[ours] = {"us": a["us"], "roofline_us": round(ideal[ours], 1),
+                          "times_roofline": round(a["us"] / ideal[ours], 2),
+                          "like": theirs, "like_us": b["us"], "like_roofline_us": round(ideal[theirs], 1),
+                          "like_times_roofline": round(b["us"] / ideal[theirs], 2)}
+    return rows
+
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -828,12 +1057,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", default="1.2b", choices=sorted(SIZES),
                     help="layer sizes: LFM2-1.2B (the default and the headline), 700M or 350M")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload", "further"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload", "further", "retorax"],
                     help="run one part only (for profiling); the JSON line then lacks the rest")
     ap.add_argument("--workloads", default="both", choices=["both", "none"] + sorted(WORKLOADS),
                     help="scheduler workloads to add to the line (default: both)")
     ap.add_argument("--workload", default="350m-mixed", choices=sorted(WORKLOADS),
                     help="with --only workload: which one")
+    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(RETORAX_SIZES),
+                    help="with --only retorax: which of the sizes")
     ap.add_argument("--kernel", default="all",
                     help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK, elementwise, copy_rate or all")
     ap.add_argument("--kernel-batch", type=int, default=64)
@@ -856,6 +1087,8 @@ def main():
         return run_kernels(args)
     if args.only == "further":
         return run_further(args)
+    if args.only == "retorax":
+        return run_designs(args)
     if args.only == "workload":
         print(json.dumps({"only": "workload", args.workload: run_workload(args.workload)}))
         return 0

@@ -12,8 +12,15 @@
 // Keys are walked in tiles of 32 aligned to absolute position 0, with a running maximum and
 // sum per head, so a position's result does not depend on how its prompt was cut.  The sink
 // enters as the initial maximum and a sum of 1.
+// Single tokens (decoding) are split over the keys: block (token, s) takes the keys of the
+// s-th stretch of AM_SPLIT positions (aligned to absolute position 0) that the token sees and
+// leaves its running maximum, sum and unnormalised values in a scratch buffer; a second kernel
+// puts a token's stretches together in order, adds the sink once, divides and gates.  Which
+// stretches a token has depends on its own position only.
 // Plain reference: tests/plain_ops.py paged_attention_mixed.
 #include "common.cuh"
+
+#define AM_SPLIT 128      // keys per block of a split launch (a multiple of AM_KT)
 
 #define AM_KT 32          // keys per tile
 #define AM_THREADS 256
@@ -47,6 +54,7 @@ __global__ void paged_attention_mixed_kernel(
     int lo = 0;
     if (window > 0) lo = max(lo, p - window + 1);
     if (chunk > 0) lo = max(lo, p / chunk * chunk);
+    const int hi = p;                                          // the block's keys: [lo, hi]
     if (mix)
         for (int i = tid; i < H * H; i += blockDim.x) mix_s[i] = mix[i];
     for (int h = tid; h < H; h += blockDim.x) {
@@ -63,11 +71,11 @@ __global__ void paged_attention_mixed_kernel(
     for (int i = 0; i < AM_MAX_ACC; ++i) acc[i] = 0.f;
     const int* table = block_table + (size_t)r * max_blocks;
     __syncthreads();
-    for (int j0 = lo / AM_KT * AM_KT; j0 <= p; j0 += AM_KT) {
+    for (int j0 = lo / AM_KT * AM_KT; j0 <= hi; j0 += AM_KT) {
         if (tid < AM_KT) {
             const int j = j0 + tid;
             long long s = -1;
-            if (j >= lo && j <= p) {
+            if (j >= lo && j <= hi) {
                 const int page = table[j / page_size];
                 if (page >= 0) s = (long long)page * page_size + j % page_size;
             }
@@ -160,12 +168,214 @@ __global__ void paged_attention_mixed_kernel(
     }
 }
 
+// Single tokens, split over the keys.  Block (token, s) stages tiles of 32 keys and values of
+// its stretch in shared memory (rows padded to an odd number of 32-bit words, so that a warp
+// whose lanes walk 32 keys meets no bank twice), forms the raw scores with a thread per (head,
+// key), mixes, keeps a running maximum and sum per head, and accumulates the values with a
+// thread per output element.
+template <typename T>
+__global__ void paged_attention_mixed_split_kernel(
+    const T* __restrict__ rows, int row_stride, const T* __restrict__ k_cache,
+    const T* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
+    const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
+    const int* __restrict__ token_req, int first_token, int H, int G, int d, int dv, int page_size,
+    float scale, int window, int chunk, const float* __restrict__ mix,
+    float* __restrict__ scratch, int n_splits) {
+    rv_pdl_launch_dependents();
+    constexpr int PER = 4 / sizeof(T);                 // elements per 32-bit word
+    const int kw = G * d / PER + 1, vw = G * dv / PER + 1;          // row lengths in words (odd: G*d, G*dv are multiples of 2*PER)
+    extern __shared__ float smem[];
+    float* q_s = smem;                                 // [H * d]
+    float* mix_s = q_s + H * d;                        // [H * H]
+    float* raw_s = mix_s + H * H;                      // [H][KT + 1]
+    float* p_s = raw_s + H * (AM_KT + 1);              // [H][KT + 1]
+    float* m_s = p_s + H * (AM_KT + 1);                // [H]
+    float* l_s = m_s + H;
+    float* alpha_s = l_s + H;
+    unsigned* kt = (unsigned*)(alpha_s + H);           // [KT][kw] words
+    unsigned* vt = kt + AM_KT * kw;                    // [KT][vw] words
+    __shared__ long long slot_s[AM_KT];
+    const int t = first_token + blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int r = token_req[t];
+    const int clen = ctx_lens[r];
+    if (clen == 0) return;                                     // a padding request
+    const int p = clen - (q_start[r + 1] - q_start[r]) + (t - q_start[r]);
+    int lo = 0;
+    if (window > 0) lo = max(lo, p - window + 1);
+    if (chunk > 0) lo = max(lo, p / chunk * chunk);
+    const int s_abs = lo / AM_SPLIT + blockIdx.y;
+    if (s_abs * AM_SPLIT > p) return;                          // the token has fewer stretches
+    lo = max(lo, s_abs * AM_SPLIT);
+    const int hi = min(p, (s_abs + 1) * AM_SPLIT - 1);
+    if (mix)
+        for (int i = tid; i < H * H; i += blockDim.x) mix_s[i] = mix[i];
+    for (int h = tid; h < H; h += blockDim.x) {
+        m_s[h] = -INFINITY;
+        l_s[h] = 0.f;
+    }
+    rv_pdl_wait();
+    const T* row = rows + (size_t)t * row_stride;
+    for (int i = tid; i < H * d; i += blockDim.x) q_s[i] = rv_load(row + i);
+    const int hpg = H / G;
+    const int n_out = H * dv;
+    float acc[AM_MAX_ACC];
+#pragma unroll
+    for (int i = 0; i < AM_MAX_ACC; ++i) acc[i] = 0.f;
+    const int* table = block_table + (size_t)r * max_blocks;
+    const int krow = G * d / PER, vrow = G * dv / PER;         // words of a key / value row
+    for (int j0 = lo / AM_KT * AM_KT; j0 <= hi; j0 += AM_KT) {
+        __syncthreads();                                       // the previous tile is used up
+        if (tid < AM_KT) {
+            const int j = j0 + tid;
+            long long s = -1;
+            if (j >= lo && j <= hi) {
+                const int page = table[j / page_size];
+                if (page >= 0) s = (long long)page * page_size + j % page_size;
+            }
+            slot_s[tid] = s;
+        }
+        __syncthreads();
+        for (int i = tid; i < AM_KT * (krow + vrow); i += blockDim.x) {
+            const int jj = i / (krow + vrow), c = i - jj * (krow + vrow);
+            const long long s = slot_s[jj];
+            if (c < krow)
+                kt[jj * kw + c] = s < 0 ? 0u : ((const unsigned*)k_cache)[(size_t)s * krow + c];
+            else
+                vt[jj * vw + c - krow] = s < 0 ? 0u : ((const unsigned*)v_cache)[(size_t)s * vrow + c - krow];
+        }
+        __syncthreads();
+        // raw scores: a warp per head, a lane per key
+        for (int h = warp; h < H; h += nwarps) {
+            const int g = h / hpg;
+            const T* kr = (const T*)(kt + lane * kw) + g * d;
+            const float* qh = q_s + h * d;
+            float dot = 0.f;
+            for (int i = 0; i < d; i += 2) {
+                float k0, k1;
+                if (sizeof(T) == 2) {
+                    const float2 kk = __bfloat1622float2(*(const __nv_bfloat162*)(kr + i));
+                    k0 = kk.x;
+                    k1 = kk.y;
+                } else {
+                    k0 = rv_load(kr + i);
+                    k1 = rv_load(kr + i + 1);
+                }
+                dot += qh[i] * k0 + qh[i + 1] * k1;
+            }
+            raw_s[h * (AM_KT + 1) + lane] = dot * scale;
+        }
+        __syncthreads();
+        for (int i = tid; i < H * AM_KT; i += blockDim.x) {
+            const int h = i / AM_KT, jj = i - h * AM_KT;
+            float v = -INFINITY;
+            if (slot_s[jj] >= 0) {
+                if (mix) {
+                    v = 0.f;
+                    for (int g = 0; g < H; ++g) v += mix_s[h * H + g] * raw_s[g * (AM_KT + 1) + jj];
+                } else {
+                    v = raw_s[h * (AM_KT + 1) + jj];
+                }
+            }
+            p_s[h * (AM_KT + 1) + jj] = v;
+        }
+        __syncthreads();
+        for (int h = warp; h < H; h += nwarps) {
+            const float v = p_s[h * (AM_KT + 1) + lane];
+            const float m_old = m_s[h];
+            const float m_new = fmaxf(m_old, rv_warp_max(v));
+            const float e = (v == -INFINITY) ? 0.f : expf(v - m_new);
+            const float sum = rv_warp_sum(e);
+            const float alpha = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+            p_s[h * (AM_KT + 1) + lane] = e;
+            if (lane == 0) {
+                m_s[h] = m_new;
+                l_s[h] = l_s[h] * alpha + sum;
+                alpha_s[h] = alpha;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < AM_MAX_ACC; ++i) {
+            const int e = tid + i * AM_THREADS;
+            if (e < n_out) {
+                const int h = e / dv, dd = e - h * dv, g = h / hpg;
+                float a = acc[i] * alpha_s[h];
+                const float* ph = p_s + h * (AM_KT + 1);
+                const T* vcol = (const T*)vt + g * dv + dd;
+                for (int jj = 0; jj < AM_KT; ++jj) a += ph[jj] * rv_load(vcol + (size_t)jj * vw * PER);
+                acc[i] = a;
+            }
+        }
+    }
+    // [token][stretch]: H maxima, H sums, H * dv unnormalised values
+    float* part = scratch + ((size_t)blockIdx.x * n_splits + blockIdx.y) * (size_t)(2 * H + n_out);
+    __syncthreads();
+    for (int h = tid; h < H; h += blockDim.x) {
+        part[h] = m_s[h];
+        part[H + h] = l_s[h];
+    }
+#pragma unroll
+    for (int i = 0; i < AM_MAX_ACC; ++i) {
+        const int e = tid + i * AM_THREADS;
+        if (e < n_out) part[2 * H + e] = acc[i];
+    }
+}
+
+// One block per single token: its stretches in order, the sink once, the division, the gate.
+template <typename T>
+__global__ void paged_attention_mixed_merge_kernel(
+    const float* __restrict__ scratch, int n_splits, const T* __restrict__ rows, int row_stride,
+    int gate_off, const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
+    const int* __restrict__ token_req, T* __restrict__ out, int first_token, int H, int dv,
+    int window, int chunk, const float* __restrict__ sinks) {
+    rv_pdl_prologue();
+    const int t = first_token + blockIdx.x;
+    const int r = token_req[t];
+    const int clen = ctx_lens[r];
+    if (clen == 0) return;
+    const int p = clen - (q_start[r + 1] - q_start[r]) + (t - q_start[r]);
+    int lo = 0;
+    if (window > 0) lo = max(lo, p - window + 1);
+    if (chunk > 0) lo = max(lo, p / chunk * chunk);
+    const int n = p / AM_SPLIT - lo / AM_SPLIT + 1;            // stretches that hold keys
+    const int n_out = H * dv;
+    const size_t stride = (size_t)(2 * H + n_out);
+    const float* base = scratch + (size_t)blockIdx.x * n_splits * stride;
+    for (int e = threadIdx.x; e < n_out; e += blockDim.x) {
+        const int h = e / dv;
+        float m = sinks ? sinks[h] : -INFINITY;
+        for (int s = 0; s < n; ++s) m = fmaxf(m, base[s * stride + h]);
+        float l = sinks ? expf(sinks[h] - m) : 0.f;
+        float a = 0.f;
+        for (int s = 0; s < n; ++s) {
+            const float ms = base[s * stride + h];
+            const float w = (ms == -INFINITY) ? 0.f : expf(ms - m);
+            l += base[s * stride + H + h] * w;
+            a += base[s * stride + 2 * H + e] * w;
+        }
+        float y = l > 0.f ? a / l : 0.f;
+        if (gate_off >= 0) y *= 1.f / (1.f + expf(-rv_load(rows + (size_t)t * row_stride + gate_off + e)));
+        rv_store(out + (size_t)t * n_out + e, y);
+    }
+}
+
+// Stretches a single token can have when it sees at most `span` keys.
+extern "C" int rv_paged_attention_mixed_splits(int span) {
+    return (span < 1 ? 1 : span + AM_SPLIT - 1) / AM_SPLIT + 1;
+}
+extern "C" long long rv_paged_attention_mixed_scratch_bytes(int n_tokens, int H, int dv, int span) {
+    return (long long)n_tokens * rv_paged_attention_mixed_splits(span) * (2ll * H + (long long)H * dv) * 4;
+}
+
 extern "C" int rv_paged_attention_mixed(
     const void* rows, int dtype, int row_stride, int gate_off, const void* k_cache,
     const void* v_cache, const int* block_table, int max_blocks, const int* q_start,
     const int* ctx_lens, const int* token_req, void* out, int first_token, int n_tokens, int H,
     int G, int d, int dv, int page_size, float scale, int window, int chunk, const float* mix,
-    const float* sinks, void* stream) {
+    const float* sinks, float* scratch, long long scratch_bytes, int span, void* stream) {
+    // `scratch` given: the tokens are single tokens that see at most `span` keys each, and every
+    // one is split over its keys
     if (n_tokens == 0) return 0;
     if (n_tokens < 0 || H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || page_size <= 0)
         RV_FAIL("paged_attention_mixed: bad sizes");
@@ -177,6 +387,33 @@ extern "C" int rv_paged_attention_mixed(
                         sizeof(long long) * AM_KT + 8;
     if (smem > 200 * 1024) RV_FAIL("paged_attention_mixed: %d heads of size %d do not fit shared memory", H, d);
     cudaStream_t s = (cudaStream_t)stream;
+    if (scratch) {
+        const int n_splits = rv_paged_attention_mixed_splits(span);
+        if (rv_paged_attention_mixed_scratch_bytes(n_tokens, H, dv, span) > scratch_bytes)
+            RV_FAIL("paged_attention_mixed: the scratch buffer is too small");
+        const int el = dtype == RV_DTYPE_BF16 ? 2 : 4;
+        if ((G * d * el) % 8 || (G * dv * el) % 8 || (uintptr_t)k_cache % 4 || (uintptr_t)v_cache % 4 || d % 2)
+            RV_FAIL("paged_attention_mixed: key and value rows of %d and %d bytes cannot be staged", G * d * el, G * dv * el);
+        const size_t ssmem = sizeof(float) * ((size_t)H * d + (size_t)H * H + 2 * (size_t)H * (AM_KT + 1) + 3 * H) +
+                             4 * (size_t)AM_KT * ((size_t)G * d * el / 4 + 1 + (size_t)G * dv * el / 4 + 1);
+        if (ssmem > 200 * 1024) RV_FAIL("paged_attention_mixed: %d heads of size %d do not fit shared memory", H, d);
+        RV_DISPATCH_DTYPE(dtype, "paged_attention_mixed", {
+            if (ssmem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(paged_attention_mixed_split_kernel<T>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ssmem);
+                if (e != cudaSuccess) RV_FAIL("paged_attention_mixed: %s", cudaGetErrorString(e));
+            }
+            rv_launch(paged_attention_mixed_split_kernel<T>, dim3(n_tokens, n_splits), dim3(AM_THREADS),
+                      ssmem, s, (const T*)rows, row_stride, (const T*)k_cache, (const T*)v_cache,
+                      block_table, max_blocks, q_start, ctx_lens, token_req, first_token, H, G, d, dv,
+                      page_size, scale, window, chunk, mix, scratch, n_splits);
+            rv_launch(paged_attention_mixed_merge_kernel<T>, dim3(n_tokens), dim3(256), 0, s,
+                      (const float*)scratch, n_splits, (const T*)rows, row_stride, gate_off, q_start,
+                      ctx_lens, token_req, (T*)out, first_token, H, dv, window, chunk, sinks);
+        });
+        RV_CHECK_LAUNCH("paged_attention_mixed");
+        return 0;
+    }
     RV_DISPATCH_DTYPE(dtype, "paged_attention_mixed", {
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(paged_attention_mixed_kernel<T>,

@@ -1,0 +1,361 @@
+// Paged attention with mixed heads for prompt portions on the tensor cores (bfloat16 storage).
+// Compiled per (key size, value size): -DRV_D=<d> -DRV_DV=<dv>, multiples of 16.
+//
+// The same function as attention_mixed.cu.  A block owns 16 query tokens of one request and
+// ALL heads of them (H a multiple of 8, at most 32; 16 H threads), because the softmax of a head
+// needs every head's scores.  Per tile of 32 keys, aligned to absolute position 0:
+//   1. keys and values of the tile come from the pages into shared memory (16-byte cp.async);
+//      the next tile's keys are requested as soon as this tile's scores are formed and its
+//      values as soon as this tile's are used, so both travel behind the arithmetic;
+//   2. warp w forms the raw scores of heads 2w, 2w+1: S_g = scale * Q_g K^T (mma.sync m16n8k16,
+//      float32 accumulators; the Q fragments stay in registers for the whole block) -> shared
+//      memory, float32;
+//   3. mixing, mask and running softmax in float32 on the CUDA cores: a thread owns 4
+//      neighbouring keys of one query token for 8 heads, s'_h = sum_g M[h, g] s_g as 32 FMAs per
+//      three 16-byte shared-memory loads, maxima and sums over a row by shuffles among the 8
+//      lanes that share the token; P goes to shared memory as bfloat16 (the row sum adds the
+//      rounded values);
+//   4. warp w rescales and extends O_h += P_h V of its two heads (V by ldmatrix.trans).
+// The sink enters as the initial maximum with a sum of 1.  The epilogue divides by the sum,
+// multiplies by sigmoid(gate) and writes bfloat16.
+// Work per (query, key) pair: 2 H (d + dv) tensor-core FLOPs and 2 H^2 float32 FLOPs for the
+// mixing, which the tensor cores cannot take in float32; from 16 heads on the mixing is the
+// longer part.
+#include "common.cuh"
+
+#ifndef RV_D
+#error "compile with -DRV_D=<key size> -DRV_DV=<value size>"
+#endif
+#if RV_D % 16 != 0 || RV_DV % 16 != 0 || RV_D > 256 || RV_DV > 256
+#error "RV_D and RV_DV must be multiples of 16, at most 256"
+#endif
+
+#define AM_KT 32
+#define AM_QT 16
+#define AM_SS 40          // float32 score row: 32 + 8 (conflict-free fragment stores)
+#define AM_PS 40          // bfloat16 probability row: 32 + 8
+
+typedef __nv_bfloat16 bf16;
+
+#define AM_CAT2(a, b, c) a##b##_##c
+#define AM_CAT(a, b, c) AM_CAT2(a, b, c)
+#define AM_NAME(base) AM_CAT(base, RV_D, RV_DV)
+
+static thread_local char g_am_error[256] = "";
+extern "C" const char* AM_NAME(rv_attention_mixed_mma_last_error_d)() { return g_am_error; }
+#define AM_FAIL(...)                                         \
+    do {                                                     \
+        snprintf(g_am_error, sizeof(g_am_error), __VA_ARGS__); \
+        return 1;                                            \
+    } while (0)
+
+__device__ __forceinline__ void am_cp_async_16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zeroed
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void am_ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void am_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT)
+attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int gate_off,
+                           const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                           const int* __restrict__ block_table, int max_blocks,
+                           const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
+                           bf16* __restrict__ out, int first_req, int H, int G, int page_size,
+                           float scale, int window, int chunk, const float* __restrict__ mix,
+                           const float* __restrict__ sinks) {
+    constexpr int D = RV_D, DV = RV_DV;
+    rv_pdl_launch_dependents();
+    const int r = first_req + blockIdx.y;
+    const int q0 = q_start[r], q_len = q_start[r + 1] - q0;
+    const int clen = ctx_lens[r];
+    const int t_first = blockIdx.x * AM_QT;                  // first query token of the block
+    if (clen == 0 || t_first >= q_len) return;
+    const int KS = G * D + 8, VS = G * DV + 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Ks = (bf16*)smem_raw;                              // [KT][KS]
+    bf16* Vs = Ks + AM_KT * KS;                              // [KT][VS]
+    float* S = (float*)(Vs + AM_KT * VS);                    // [H][QT][SS]
+    bf16* P = (bf16*)(S + (size_t)H * AM_QT * AM_SS);        // [H][QT][PS]
+    float* Tt = (float*)(P + (size_t)H * AM_QT * AM_PS);     // [H][H]: Tt[g][h] = mix[h][g]
+    float* alpha_s = Tt + H * H;                             // [H][QT]
+    float* l_s = alpha_s + H * AM_QT;                        // [H][QT] running sums
+    float* m_s = l_s + H * AM_QT;                            // [H][QT] running maxima
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hpg = H / G;
+    for (int i = tid; i < H * H; i += blockDim.x) {
+        const int g = i / H, h = i - g * H;
+        Tt[i] = mix ? mix[h * H + g] : (g == h ? 1.f : 0.f);
+    }
+    const int p_first = clen - q_len + t_first;              // position of the block's first query
+    const int n_q = min(AM_QT, q_len - t_first);
+    // what the mixing thread owns: 8 heads, one query token, 4 neighbouring keys of a tile
+    const int hb = tid >> 7, mq = (tid & 127) >> 3, kg = tid & 7;
+    const int mp = p_first + mq;                             // its query's position
+    int mlo = 0;
+    if (window > 0) mlo = max(mlo, mp - window + 1);
+    if (chunk > 0) mlo = max(mlo, mp / chunk * chunk);
+    const bool mq_live = mq < n_q;
+    // running maximum and sum of a (head, token): read by the 8 lanes that share the token,
+    // written by the first of them; a tile touches each once, between two block barriers
+    if (kg == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            m_s[(hb * 8 + j) * AM_QT + mq] = sinks ? sinks[hb * 8 + j] : -INFINITY;
+            l_s[(hb * 8 + j) * AM_QT + mq] = sinks ? 1.f : 0.f;
+        }
+    }
+    int lo_first = 0;                                        // lowest key any query of the block sees
+    if (window > 0) lo_first = max(lo_first, p_first - window + 1);
+    if (chunk > 0) lo_first = max(lo_first, p_first / chunk * chunk);
+    const int p_last = p_first + n_q - 1;
+    const int* table = block_table + (size_t)r * max_blocks;
+    rv_pdl_wait();
+
+    // Q fragments of this warp's two heads
+    unsigned qf[2][D / 16][4];
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int h = 2 * warp + hh;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const bf16* base = rows + (size_t)(q0 + t_first) * row_stride + (size_t)h * D + ks * 16 + c0;
+                const unsigned z = 0u;
+                qf[hh][ks][0] = r0 < n_q ? *(const unsigned*)(base + (size_t)r0 * row_stride) : z;
+                qf[hh][ks][1] = r0 + 8 < n_q ? *(const unsigned*)(base + (size_t)(r0 + 8) * row_stride) : z;
+                qf[hh][ks][2] = r0 < n_q ? *(const unsigned*)(base + (size_t)r0 * row_stride + 8) : z;
+                qf[hh][ks][3] = r0 + 8 < n_q ? *(const unsigned*)(base + (size_t)(r0 + 8) * row_stride + 8) : z;
+            }
+        }
+    }
+    float o[2][DV / 8][4];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[hh][nt][i] = 0.f;
+
+    // keys of tile j0 into Ks / values into Vs: 16-byte pieces, zeros where nothing is seen
+    auto load_tile = [&](int j0, bool keys) {
+        const int chunks = (keys ? G * D : G * DV) / 8;
+        bf16* dst = keys ? Ks : Vs;
+        const bf16* src = keys ? k_cache : v_cache;
+        const int stride = keys ? KS : VS;
+        if (j0 <= p_last)
+            for (int i = tid; i < AM_KT * chunks; i += blockDim.x) {
+                const int jj = i / chunks, c = i - jj * chunks;
+                const int j = j0 + jj;
+                bool valid = j >= lo_first && j <= p_last;
+                long long slot = 0;
+                if (valid) {
+                    const int page = table[j / page_size];
+                    valid = page >= 0;
+                    slot = (long long)page * page_size + j % page_size;
+                }
+                am_cp_async_16(dst + jj * stride + c * 8, src + ((size_t)slot * chunks + c) * 8, valid);
+            }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    const int j_first = lo_first / AM_KT * AM_KT;
+    load_tile(j_first, true);
+    load_tile(j_first, false);
+    for (int j0 = j_first; j0 <= p_last; j0 += AM_KT) {
+        // 1. the tile's keys have landed (its values may still be on their way)
+        asm volatile("cp.async.wait_group 1;\n" ::);
+        __syncthreads();
+        // 2. raw scores of this warp's heads
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int h = 2 * warp + hh, g = h / hpg;
+            float* Sh = S + (size_t)h * AM_QT * AM_SS;
+#pragma unroll
+            for (int nt = 0; nt < AM_KT / 8; ++nt) {
+                float c[4] = {0.f, 0.f, 0.f, 0.f};
+                const bf16* kb = Ks + (nt * 8 + (lane >> 2)) * KS + g * D + (lane & 3) * 2;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                    am_mma(c, qf[hh][ks], *(const unsigned*)(kb + ks * 16), *(const unsigned*)(kb + ks * 16 + 8));
+                const int col = nt * 8 + (lane & 3) * 2;
+                *(float2*)(Sh + (lane >> 2) * AM_SS + col) = make_float2(c[0] * scale, c[1] * scale);
+                *(float2*)(Sh + ((lane >> 2) + 8) * AM_SS + col) = make_float2(c[2] * scale, c[3] * scale);
+            }
+        }
+        __syncthreads();
+        load_tile(j0 + AM_KT, true);          // the next tile's keys travel during the mixing
+        // 3. mixing, mask, running softmax
+        {
+            float acc[8][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+            const float* sp = S + mq * AM_SS + kg * 4;
+            const float* tp = Tt + hb * 8;
+            for (int g = 0; g < H; ++g) {
+                const float4 s = *(const float4*)(sp + (size_t)g * AM_QT * AM_SS);
+                const float4 ta = *(const float4*)(tp + g * H), tb = *(const float4*)(tp + g * H + 4);
+                const float tv[8] = {ta.x, ta.y, ta.z, ta.w, tb.x, tb.y, tb.z, tb.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    acc[j][0] += tv[j] * s.x;
+                    acc[j][1] += tv[j] * s.y;
+                    acc[j][2] += tv[j] * s.z;
+                    acc[j][3] += tv[j] * s.w;
+                }
+            }
+            bool see[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int j = j0 + kg * 4 + i;
+                see[i] = mq_live && j >= mlo && j <= mp;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float mx = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx = fmaxf(mx, see[i] ? acc[j][i] : -INFINITY);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                const int h = hb * 8 + j;
+                const float m_old = m_s[h * AM_QT + mq], l_old = l_s[h * AM_QT + mq];
+                __syncwarp();
+                const float m_new = fmaxf(m_old, mx);
+                float e[4];
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    e[i] = (see[i] && m_new != -INFINITY) ? expf(acc[j][i] - m_new) : 0.f;
+                    e[i] = __bfloat162float(__float2bfloat16_rn(e[i]));
+                    sum += e[i];
+                }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                const float alpha = (m_old == -INFINITY) ? (m_new == -INFINITY ? 1.f : 0.f)
+                                                         : expf(m_old - m_new);
+                const __nv_bfloat162 p01 = __floats2bfloat162_rn(e[0], e[1]), p23 = __floats2bfloat162_rn(e[2], e[3]);
+                uint2 pk;
+                pk.x = *(const unsigned*)&p01;
+                pk.y = *(const unsigned*)&p23;
+                *(uint2*)(P + ((size_t)h * AM_QT + mq) * AM_PS + kg * 4) = pk;
+                if (kg == 0) {
+                    alpha_s[h * AM_QT + mq] = alpha;
+                    m_s[h * AM_QT + mq] = m_new;
+                    l_s[h * AM_QT + mq] = l_old * alpha + sum;
+                }
+            }
+        }
+        asm volatile("cp.async.wait_group 1;\n" ::);      // this tile's values have landed
+        __syncthreads();
+        // 4. O_h = alpha O_h + P_h V for this warp's heads
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int h = 2 * warp + hh, g = h / hpg;
+            const float a_lo = alpha_s[h * AM_QT + (lane >> 2)], a_hi = alpha_s[h * AM_QT + (lane >> 2) + 8];
+#pragma unroll
+            for (int nt = 0; nt < DV / 8; ++nt) {
+                o[hh][nt][0] *= a_lo; o[hh][nt][1] *= a_lo;
+                o[hh][nt][2] *= a_hi; o[hh][nt][3] *= a_hi;
+            }
+            const bf16* Ph = P + (size_t)h * AM_QT * AM_PS;
+#pragma unroll
+            for (int ks = 0; ks < AM_KT / 16; ++ks) {
+                unsigned a[4];
+                const bf16* pb = Ph + (lane >> 2) * AM_PS + ks * 16 + (lane & 3) * 2;
+                a[0] = *(const unsigned*)pb;
+                a[1] = *(const unsigned*)(pb + 8 * AM_PS);
+                a[2] = *(const unsigned*)(pb + 8);
+                a[3] = *(const unsigned*)(pb + 8 * AM_PS + 8);
+#pragma unroll
+                for (int nt = 0; nt < DV / 8; nt += 2) {
+                    unsigned b[4];
+                    // matrices: (keys 0..7, nt), (keys 8..15, nt), (keys 0..7, nt+1), (keys 8..15, nt+1)
+                    const bf16* vb = Vs + (ks * 16 + (lane & 15)) * VS + g * DV + (nt + (lane >> 4)) * 8;
+                    am_ldmatrix_x4_trans(b, vb);
+                    am_mma(o[hh][nt], a, b[0], b[1]);
+                    am_mma(o[hh][nt + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+        load_tile(j0 + AM_KT, false);         // the next tile's values travel during its scores
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    const int n_out = H * DV;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int h = 2 * warp + hh;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = (lane >> 2) + 8 * half;
+            if (row >= n_q) continue;
+            const float l = l_s[h * AM_QT + row];
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const size_t t = (size_t)(q0 + t_first + row);
+#pragma unroll
+            for (int nt = 0; nt < DV / 8; ++nt) {
+                const int e = h * DV + nt * 8 + (lane & 3) * 2;
+                float y0 = o[hh][nt][2 * half] * inv, y1 = o[hh][nt][2 * half + 1] * inv;
+                if (gate_off >= 0) {
+                    const float2 gt = __bfloat1622float2(*(const __nv_bfloat162*)(rows + t * row_stride + gate_off + e));
+                    y0 *= 1.f / (1.f + expf(-gt.x));
+                    y1 *= 1.f / (1.f + expf(-gt.y));
+                }
+                *(__nv_bfloat162*)(out + t * n_out + e) = __floats2bfloat162_rn(y0, y1);
+            }
+        }
+    }
+}
+
+extern "C" long long AM_NAME(rv_attention_mixed_mma_smem_d)(int H, int G) {
+    return (long long)AM_KT * (G * RV_D + 8) * 2 + (long long)AM_KT * (G * RV_DV + 8) * 2 +
+           (long long)H * AM_QT * AM_SS * 4 + (long long)H * AM_QT * AM_PS * 2 + (long long)H * H * 4 +
+           3ll * H * AM_QT * 4;
+}
+
+// Requests [first_req, first_req + n_reqs) bring `max_q_len` tokens at most.
+extern "C" int AM_NAME(rv_attention_mixed_mma_d)(
+    const void* rows, int row_stride, int gate_off, const void* k_cache, const void* v_cache,
+    const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens, void* out,
+    int first_req, int n_reqs, int max_q_len, int H, int G, int page_size, float scale, int window,
+    int chunk, const float* mix, const float* sinks, void* stream) {
+    if (n_reqs <= 0 || max_q_len <= 0) return 0;
+    if (H <= 0 || H % 8 || H > 32 || G <= 0 || H % G) AM_FAIL("attention_mixed_mma: %d heads (multiples of 8 up to 32) over %d key/value heads", H, G);
+    if (row_stride % 2 || (gate_off >= 0 && gate_off % 2) || ((uintptr_t)rows % 4) || ((uintptr_t)out % 4) ||
+        ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16))
+        AM_FAIL("attention_mixed_mma: rows or pages are not aligned");
+    const long long smem = AM_NAME(rv_attention_mixed_mma_smem_d)(H, G);
+    if (smem > 227 * 1024) AM_FAIL("attention_mixed_mma: %lld bytes of shared memory", smem);
+    // up to 16 heads a block has 256 threads and the compiler all the registers it wants; above,
+    // 512 threads of 128 registers
+    auto kernel = H <= 16 ? attention_mixed_mma_kernel<256> : attention_mixed_mma_kernel<512>;
+    static long long configured[2] = {0, 0};
+    if (smem > configured[H > 16]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) AM_FAIL("attention_mixed_mma: %s", cudaGetErrorString(e));
+        configured[H > 16] = smem;
+    }
+    rv_launch(kernel, dim3((max_q_len + AM_QT - 1) / AM_QT, n_reqs), dim3(16 * H),
+              (size_t)smem, (cudaStream_t)stream, (const bf16*)rows, row_stride, gate_off,
+              (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, q_start, ctx_lens,
+              (bf16*)out, first_req, H, G, page_size, scale, window, chunk, mix, sinks);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) AM_FAIL("attention_mixed_mma: %s", cudaGetErrorString(e));
+    return 0;
+}

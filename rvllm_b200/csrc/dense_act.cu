@@ -22,6 +22,24 @@ __global__ void xielu_kernel(const T* __restrict__ in, const float* __restrict__
         rv_store(out + i, rv_xielu(rv_load(in + i), ap, an));
 }
 
+// For results that are rounded to bfloat16: e^z - 1 - z without the library's expm1f.  Below
+// -1/2 the difference e^z - 1 loses nothing; above, the series z^2/2 + ... + z^8/8! (its first
+// missing term is below 2^-27 there).  Both sides are evaluated, so a warp does not diverge.
+__device__ __forceinline__ float rv_xielu_bf16(float z, float ap, float an) {
+    const float zn = fminf(z, 0.f);
+    float ser = 1.f / 40320.f;
+    ser = fmaf(ser, zn, 1.f / 5040.f);
+    ser = fmaf(ser, zn, 1.f / 720.f);
+    ser = fmaf(ser, zn, 1.f / 120.f);
+    ser = fmaf(ser, zn, 1.f / 24.f);
+    ser = fmaf(ser, zn, 1.f / 6.f);
+    ser = fmaf(ser, zn, 0.5f);
+    ser *= zn * zn;
+    const float far = __expf(zn) - 1.f - zn;
+    const float neg = an * (zn < -0.5f ? far : ser);
+    return fmaf(0.5f, z, z > 0.f ? ap * z * z : neg);
+}
+
 // bfloat16, eight values per 16-byte access
 __global__ void xielu_bf16x8_kernel(const uint4* __restrict__ in, const float* __restrict__ act,
                                     uint4* __restrict__ out, size_t total8) {
@@ -37,7 +55,7 @@ __global__ void xielu_bf16x8_kernel(const uint4* __restrict__ in, const float* _
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const float2 z = __bfloat1622float2(x2[k]);
-            o2[k] = __floats2bfloat162_rn(rv_xielu(z.x, ap, an), rv_xielu(z.y, ap, an));
+            o2[k] = __floats2bfloat162_rn(rv_xielu_bf16(z.x, ap, an), rv_xielu_bf16(z.y, ap, an));
         }
         out[i] = o4;
     }

@@ -10,10 +10,14 @@
 // the recurrence S_t = a_t S_(t-1) + b_t is linear, so a block of (chunks x channels) threads lets
 // every thread reduce its chunk of LEN tokens to (A, B) with S_end = A S_begin + B, walks the
 // chunks' (A, B) in order through shared memory to get each chunk's S_begin, and then runs its
-// chunk again from S_begin.  Within one step the association of the sums differs from the serial
+// chunk again from S_begin (chunks of up to 16 tokens keep their gates in registers instead of
+// forming them twice).  Within one step the association of the sums differs from the serial
 // order only by float32 rounding.
 // Plain reference: tests/plain_ops.py mingru_scan.
 #include "common.cuh"
+
+#define RV_MINGRU_CHUNKED_FROM 64
+#define RV_MINGRU_KEEP 16          // chunks up to this many tokens keep their gates in registers
 
 __device__ __forceinline__ float rv_sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
 
@@ -54,7 +58,7 @@ __global__ void mingru_serial_kernel(const float* __restrict__ rows, const float
 // blockDim = (CH channels, NC chunks); a request's portion is cut into NC chunks of
 // len = ceil(T / NC) tokens.
 template <typename TO, int CH, int NC>
-__global__ void mingru_chunked_kernel(const float* __restrict__ rows, const float* __restrict__ bias,
+__global__ void __launch_bounds__(CH * NC) mingru_chunked_kernel(const float* __restrict__ rows, const float* __restrict__ bias,
                                       float* __restrict__ state, const int* __restrict__ q_start,
                                       const int* __restrict__ state_slot, TO* __restrict__ out,
                                       int width, int min_len) {
@@ -72,6 +76,36 @@ __global__ void mingru_chunked_kernel(const float* __restrict__ rows, const floa
     const int len = (t1 - t0 + NC - 1) / NC;
     const int b0 = min(t0 + k * len, t1), b1 = min(b0 + len, t1);
     float A = 1.f, B = 0.f;
+    if (len <= RV_MINGRU_KEEP) {
+        // short chunks: the gates of the first pass stay in registers for the second
+        float ka[RV_MINGRU_KEEP], kb[RV_MINGRU_KEEP];
+#pragma unroll
+        for (int i = 0; i < RV_MINGRU_KEEP; ++i) {
+            ka[i] = 1.f;
+            kb[i] = 0.f;
+            if (live && b0 + i < b1) {
+                const float* row = rows + (size_t)(b0 + i) * 3 * width;
+                mingru_gate(row[c], row[width + c], bz, bx, ka[i], kb[i]);
+                A *= ka[i];
+                B = ka[i] * B + kb[i];
+            }
+        }
+        sa[k][threadIdx.x] = A;
+        sb[k][threadIdx.x] = B;
+        __syncthreads();
+        float s = live ? state[(size_t)slot * width + c] : 0.f;
+        for (int j = 0; j < k; ++j) s = sa[j][threadIdx.x] * s + sb[j][threadIdx.x];
+        if (!live) return;
+#pragma unroll
+        for (int i = 0; i < RV_MINGRU_KEEP; ++i)
+            if (b0 + i < b1) {
+                s = ka[i] * s + kb[i];
+                const float g = rows[(size_t)(b0 + i) * 3 * width + 2 * width + c];
+                rv_store(out + (size_t)(b0 + i) * width + c, s * (g * rv_sigmoid(g)));
+            }
+        if (k == NC - 1) state[(size_t)slot * width + c] = s;
+        return;
+    }
     if (live)
         for (int t = b0; t < b1; ++t) {
             const float* row = rows + (size_t)t * 3 * width;
@@ -97,7 +131,6 @@ __global__ void mingru_chunked_kernel(const float* __restrict__ rows, const floa
     if (k == NC - 1) state[(size_t)slot * width + c] = s;
 }
 
-#define RV_MINGRU_CHUNKED_FROM 64
 
 extern "C" int rv_mingru_scan(const float* rows, const float* bias, float* state,
                               const int* q_start, const int* state_slot, void* out, int out_dtype,
@@ -112,8 +145,14 @@ extern "C" int rv_mingru_scan(const float* rows, const float* bias, float* state
         rv_launch(mingru_serial_kernel<T>, dim3((width + 127) / 128, n_reqs), dim3(128), 0, s, rows,
                   bias, state, q_start, state_slot, (T*)out, width, 0,
                   chunked ? RV_MINGRU_CHUNKED_FROM - 1 : 0x7fffffff);
-        if (chunked)
+        // narrower channel tiles for narrower models, so that one long prompt still fills the
+        // GPU (the tile follows from the width alone, never from what else is in the batch)
+        if (chunked && width >= 4096)
             rv_launch(mingru_chunked_kernel<T, 32, 32>, dim3((width + 31) / 32, n_reqs), dim3(32, 32),
+                      0, s, rows, bias, state, q_start, state_slot, (T*)out, width,
+                      RV_MINGRU_CHUNKED_FROM);
+        else if (chunked)
+            rv_launch(mingru_chunked_kernel<T, 8, 128>, dim3((width + 7) / 8, n_reqs), dim3(8, 128),
                       0, s, rows, bias, state, q_start, state_slot, (T*)out, width,
                       RV_MINGRU_CHUNKED_FROM);
     });

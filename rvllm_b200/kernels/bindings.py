@@ -50,6 +50,7 @@ class CudaOps:
         self.lib.rv_last_error.restype = ctypes.c_char_p
         self.lib.rv_paged_attention_decode_scratch_bytes.restype = c_longlong
         self.lib.rv_gemm_tiled_bytes.restype = c_longlong
+        self.lib.rv_paged_attention_mixed_scratch_bytes.restype = c_longlong
         self._scratch = {}
         self._retired = []
         self._attn_libs = {}
@@ -697,14 +698,96 @@ class CudaOps:
             self._need(sinks, "sinks", torch.float32)
         if out.shape[1] != num_heads * v_head_dim:
             raise KernelError("paged_attention_mixed: output width and head sizes disagree")
-        self._check(self.lib.rv_paged_attention_mixed(
-            _ptr(rows), _code(rows.dtype), c_int(rows.shape[1]), c_int(gate_off), _ptr(k_cache),
-            _ptr(v_cache), _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
-            _ptr(ctx.ctx_lens), _ptr(ctx.token_req), _ptr(out), c_int(0), c_int(ctx.n_tokens),
-            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(v_head_dim),
-            c_int(group.page_size), c_float(scale), c_int(window if window else 0),
-            c_int(chunk if chunk else 0), _ptr(head_mix), _ptr(sinks), self._stream()),
-            "paged_attention_mixed")
+        nd = ctx.n_decode
+        tensor = ctx.n_tokens > nd and self._mixed_mma_ok(rows, num_heads, num_kv_heads, head_dim,
+                                                          v_head_dim, gate_off)
+        # single tokens, and everything the tensor-core kernel does not take: one block a token
+        def simt(first, count, scratch=None, span=0):
+            self._check(self.lib.rv_paged_attention_mixed(
+                _ptr(rows), _code(rows.dtype), c_int(rows.shape[1]), c_int(gate_off), _ptr(k_cache),
+                _ptr(v_cache), _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
+                _ptr(ctx.ctx_lens), _ptr(ctx.token_req), _ptr(out), c_int(first), c_int(count),
+                c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(v_head_dim),
+                c_int(group.page_size), c_float(scale), c_int(window if window else 0),
+                c_int(chunk if chunk else 0), _ptr(head_mix), _ptr(sinks), _ptr(scratch),
+                c_longlong(scratch.numel() if scratch is not None else 0), c_int(span),
+                self._stream()), "paged_attention_mixed")
+
+        el = rows.element_size()
+        staged = (num_kv_heads * head_dim * el) % 8 == 0 and (num_kv_heads * v_head_dim * el) % 8 == 0 \
+            and head_dim % 2 == 0 and 4 * (num_heads * (head_dim + num_heads + 70) + 8 * num_kv_heads
+                                           * (head_dim + v_head_dim) * el + 64) <= 200 * 1024
+        if nd > 0 and staged:
+            # single tokens: each split over the keys it sees, then put together
+            span = self._mixed_span(ctx.max_ctx_len, window, chunk)
+            need = self.attention_mixed_scratch_bytes(nd, num_heads, v_head_dim, span)
+            simt(0, nd, self._scratch_buffer(need, rows.device), span)
+            self.launches += 1
+        elif nd > 0:
+            simt(0, nd)                    # rows that cannot be staged: one block a token
+        if ctx.n_tokens > nd and not tensor:
+            simt(nd, ctx.n_tokens - nd)
+        if tensor:
+            lib = self._mixed_lib(head_dim, v_head_dim)
+            tag = f"{head_dim}_{v_head_dim}"
+            rc = getattr(lib, f"rv_attention_mixed_mma_d{tag}")(
+                _ptr(rows), c_int(rows.shape[1]), c_int(gate_off), _ptr(k_cache), _ptr(v_cache),
+                _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
+                _ptr(ctx.ctx_lens), _ptr(out), c_int(nd), c_int(ctx.n_reqs - nd),
+                c_int(ctx.max_q_len), c_int(num_heads), c_int(num_kv_heads),
+                c_int(group.page_size), c_float(scale), c_int(window if window else 0),
+                c_int(chunk if chunk else 0), _ptr(head_mix), _ptr(sinks), self._stream())
+            self.launches += 1
+            if rc != 0:
+                msg = getattr(lib, f"rv_attention_mixed_mma_last_error_d{tag}")().decode()
+                raise KernelError(f"paged_attention_mixed: {msg}")
+
+    @staticmethod
+    def _mixed_span(max_ctx_len, window, chunk) -> int:
+        """The most keys a token can see."""
+        span = max(1, int(max_ctx_len))
+        if window:
+            span = min(span, window)
+        if chunk:
+            span = min(span, chunk)
+        return span
+
+    def attention_mixed_scratch_bytes(self, n_tokens, num_heads, v_head_dim, span) -> int:
+        """Scratch of the split launch for `n_tokens` single tokens that see `span` keys at most."""
+        return int(self.lib.rv_paged_attention_mixed_scratch_bytes(
+            c_int(n_tokens), c_int(num_heads), c_int(v_head_dim), c_int(span)))
+
+    def _mixed_mma_ok(self, rows, num_heads, num_kv_heads, head_dim, v_head_dim, gate_off) -> bool:
+        """Whether prompt portions go to the tensor-core kernel (attention_mixed_mma.cu):
+        bfloat16, head counts in multiples of 8 up to 32, sizes in multiples of 16, and a
+        block's tiles within shared memory.  RVLLM_MIXED_ATTENTION=simt: never."""
+        if os.environ.get("RVLLM_MIXED_ATTENTION", "auto") == "simt":
+            return False
+        if rows.dtype != torch.bfloat16 or num_heads % 8 or num_heads > 32:
+            return False
+        if head_dim % 16 or v_head_dim % 16 or head_dim > 256 or v_head_dim > 256:
+            return False
+        if rows.shape[1] % 2 or (gate_off >= 0 and gate_off % 2):
+            return False
+        smem = 32 * (num_kv_heads * (head_dim + v_head_dim) + 16) * 2 \
+            + num_heads * 16 * 40 * 6 + num_heads * num_heads * 4 + num_heads * 192
+        return smem <= 227 * 1024
+
+    def _mixed_lib(self, head_dim: int, v_head_dim: int):
+        """The tensor-core mixed-head attention library for these sizes, built at first use."""
+        key = ("mixed", head_dim, v_head_dim)
+        lib = self._attn_libs.get(key)
+        if lib is None:
+            tag = f"{head_dim}_{v_head_dim}"
+            path = build_variant("attention_mixed_mma.cu", {"RV_D": head_dim, "RV_DV": v_head_dim},
+                                 f"attnmix_d{tag}", verbose=self._verbose_build)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+            getattr(lib, f"rv_attention_mixed_mma_last_error_d{tag}").restype = ctypes.c_char_p
+            self._attn_libs[key] = lib
+        return lib
 
     # ---- sampling --------------------------------------------------------------------
 

@@ -68,7 +68,8 @@ class MixedAttention(Mixer):
         sizer = getattr(ops, "attention_mixed_scratch_bytes", None)
         if sizer is None:
             return 0
-        return sizer(max_requests, spec.num_heads, MixedAttention._vd(spec), max_context)
+        span = min(x for x in (max_context, spec.window, spec.chunk) if x)
+        return sizer(max_requests, spec.num_heads, MixedAttention._vd(spec), span)
 
     def __init__(self, spec: MixedAttentionSpec, tensors, ops, dtype):
         if spec.num_heads % spec.num_kv_heads:

@@ -51,11 +51,13 @@ def mingru(h, t, state=None):
 
 
 def rotate(x, positions, dims, base):
-    """x: [T, heads, d]; the first `dims` dimensions of every head turn, i with i + dims/2."""
+    """x: [T, heads, d]; the first `dims` dimensions of every head turn, i with i + dims/2.
+    The design forms positions and angles in float32: the angle is the float32 product of the
+    position and the float32 frequency (its sine and cosine are then taken in x's type)."""
     half = dims // 2
-    i = torch.arange(half, dtype=x.dtype)
-    f = base ** (-2.0 * i / dims)
-    a = positions.to(x.dtype)[:, None] * f[None, :]
+    i = torch.arange(half, dtype=torch.float64)
+    f = (base ** (-2.0 * i / dims)).to(torch.float32)
+    a = (positions.to(torch.float32)[:, None] * f[None, :]).to(x.dtype)
     cos, sin = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
     u, v = x[..., :half], x[..., half:dims]
     out = x.clone()
@@ -74,28 +76,39 @@ def attention_keys_values(h, t, m):
     return k, v
 
 
+def attention_core(q, k, v, scale, talk=None, sink=None, chunk=None, window=None, first=0):
+    """q: [T, H, d] rotated queries at positions first..first+T-1; k: [S, G, d], v: [S, G, dv]
+    for positions 0..S-1 (S >= first + T).  Returns [T, H, dv]."""
+    T, H = q.shape[0], q.shape[1]
+    S, G = k.shape[0], k.shape[1]
+    kv_of = torch.arange(H) // (H // G)
+    raw = torch.einsum("ihd,jhd->hij", q, k[:, kv_of, :]) * scale
+    mixed = raw if talk is None else torch.einsum("hg,gij->hij", talk, raw)
+    i, j = (first + torch.arange(T))[:, None], torch.arange(S)[None, :]
+    see = j <= i
+    if chunk:
+        see = see & (i // chunk == j // chunk)
+    if window:
+        see = see & (j > i - window)
+    mixed = mixed.masked_fill(~see[None], -math.inf)
+    top = mixed.max(-1).values
+    if sink is not None:
+        top = torch.maximum(top, sink[:, None])
+    e = torch.exp(mixed - top[..., None])
+    denom = e.sum(-1)
+    if sink is not None:
+        denom = denom + torch.exp(sink[:, None] - top)
+    return torch.einsum("hij,jhd->ihd", e / denom[..., None], v[:, kv_of, :])
+
+
 def attention(h, t, m, k, v):
     """t: the mixer's tensors (q, talk, sink, g, o); k, v: keys and values of all positions,
     this layer's own or another layer's."""
     T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    pos = torch.arange(T)
-    q = rotate((h @ t["q"].T).view(T, H, d), pos, m["rot"]["dims"], m["rot"]["base"])
-    kv_of = torch.arange(H) // (H // G)
-    # raw[h, i, j]
-    raw = torch.einsum("ihd,jhd->hij", q, k[:, kv_of, :]) * m["scale"]
-    mixed = torch.einsum("hg,gij->hij", t["talk"], raw)
-    i, j = pos[:, None], pos[None, :]
-    see = j <= i
-    size = (m.get("mask") or {}).get("size")
-    if size:
-        see = see & (i // size == j // size)
-    mixed = mixed.masked_fill(~see[None], -math.inf)
-    top = torch.maximum(mixed.max(-1).values, t["sink"][:, None])          # [H, T]
-    e = torch.exp(mixed - top[..., None])
-    denom = e.sum(-1) + torch.exp(t["sink"][:, None] - top)
-    w = e / denom[..., None]
-    heads = torch.einsum("hij,jhd->ihd", w, v[:, kv_of, :]).reshape(T, H * dv)
+    H, d, dv = m["heads"], m["dim"], m["vdim"]
+    q = rotate((h @ t["q"].T).view(T, H, d), torch.arange(T), m["rot"]["dims"], m["rot"]["base"])
+    heads = attention_core(q, k, v, m["scale"], t["talk"], t["sink"],
+                           (m.get("mask") or {}).get("size")).reshape(T, H * dv)
     heads = heads * torch.sigmoid(h @ t["g"].T)
     return heads @ t["o"].T
 
