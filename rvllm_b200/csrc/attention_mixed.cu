@@ -224,6 +224,8 @@ __global__ void paged_attention_mixed_split_kernel(
     for (int i = 0; i < AM_MAX_ACC; ++i) acc[i] = 0.f;
     const int* table = block_table + (size_t)r * max_blocks;
     const int krow = G * d / PER, vrow = G * dv / PER;         // words of a key / value row
+    const bool vec16 = krow % 4 == 0 && vrow % 4 == 0 && (uintptr_t)k_cache % 16 == 0 &&
+                       (uintptr_t)v_cache % 16 == 0;
     for (int j0 = lo / AM_KT * AM_KT; j0 <= hi; j0 += AM_KT) {
         __syncthreads();                                       // the previous tile is used up
         if (tid < AM_KT) {
@@ -236,13 +238,42 @@ __global__ void paged_attention_mixed_split_kernel(
             slot_s[tid] = s;
         }
         __syncthreads();
-        for (int i = tid; i < AM_KT * (krow + vrow); i += blockDim.x) {
-            const int jj = i / (krow + vrow), c = i - jj * (krow + vrow);
-            const long long s = slot_s[jj];
-            if (c < krow)
-                kt[jj * kw + c] = s < 0 ? 0u : ((const unsigned*)k_cache)[(size_t)s * krow + c];
-            else
-                vt[jj * vw + c - krow] = s < 0 ? 0u : ((const unsigned*)v_cache)[(size_t)s * vrow + c - krow];
+        if (vec16) {
+            // 16-byte loads, four in flight per thread before any is stored
+            const int kq = krow / 4, vq = vrow / 4, per = kq + vq, total = AM_KT * per;
+            for (int base = tid; base < total; base += 4 * blockDim.x) {
+                uint4 val[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = base + u * blockDim.x;
+                    val[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (i < total) {
+                        const int jj = i / per, c = i - jj * per;
+                        const long long s = slot_s[jj];
+                        if (s >= 0)
+                            val[u] = c < kq ? ((const uint4*)k_cache)[(size_t)s * kq + c]
+                                            : ((const uint4*)v_cache)[(size_t)s * vq + c - kq];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = base + u * blockDim.x;
+                    if (i < total) {
+                        const int jj = i / per, c = i - jj * per;
+                        unsigned* dst = c < kq ? kt + jj * kw + 4 * c : vt + jj * vw + 4 * (c - kq);
+                        dst[0] = val[u].x; dst[1] = val[u].y; dst[2] = val[u].z; dst[3] = val[u].w;
+                    }
+                }
+            }
+        } else {
+            for (int i = tid; i < AM_KT * (krow + vrow); i += blockDim.x) {
+                const int jj = i / (krow + vrow), c = i - jj * (krow + vrow);
+                const long long s = slot_s[jj];
+                if (c < krow)
+                    kt[jj * kw + c] = s < 0 ? 0u : ((const unsigned*)k_cache)[(size_t)s * krow + c];
+                else
+                    vt[jj * vw + c - krow] = s < 0 ? 0u : ((const unsigned*)v_cache)[(size_t)s * vrow + c - krow];
+            }
         }
         __syncthreads();
         // raw scores: a warp per head, a lane per key
@@ -328,17 +359,23 @@ __global__ void paged_attention_mixed_merge_kernel(
     const float* __restrict__ scratch, int n_splits, const T* __restrict__ rows, int row_stride,
     int gate_off, const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
     const int* __restrict__ token_req, T* __restrict__ out, int first_token, int H, int dv,
-    int window, int chunk, const float* __restrict__ sinks) {
+    int window, int chunk, const float* __restrict__ sinks, int stretch, int tile) {
+    // `tile`: how many neighbouring tokens of a request shared one block of the split launch
+    // (1: single tokens; 16: the tensor-core kernel's query tiles, counted from the request's
+    // first token of the step); the stretches that ran are those the whole tile can see
     rv_pdl_prologue();
     const int t = first_token + blockIdx.x;
     const int r = token_req[t];
     const int clen = ctx_lens[r];
     if (clen == 0) return;
-    const int p = clen - (q_start[r + 1] - q_start[r]) + (t - q_start[r]);
+    const int q_len = q_start[r + 1] - q_start[r];
+    const int in_tile = (t - q_start[r]) % tile;
+    const int p_first = clen - q_len + (t - q_start[r]) - in_tile;
+    const int p = min(p_first + tile - 1, clen - 1);           // the tile's last position
     int lo = 0;
-    if (window > 0) lo = max(lo, p - window + 1);
-    if (chunk > 0) lo = max(lo, p / chunk * chunk);
-    const int n = p / AM_SPLIT - lo / AM_SPLIT + 1;            // stretches that hold keys
+    if (window > 0) lo = max(lo, p_first - window + 1);
+    if (chunk > 0) lo = max(lo, p_first / chunk * chunk);
+    const int n = p / stretch - lo / stretch + 1;              // stretches that ran
     const int n_out = H * dv;
     const size_t stride = (size_t)(2 * H + n_out);
     const float* base = scratch + (size_t)blockIdx.x * n_splits * stride;
@@ -366,6 +403,25 @@ extern "C" int rv_paged_attention_mixed_splits(int span) {
 }
 extern "C" long long rv_paged_attention_mixed_scratch_bytes(int n_tokens, int H, int dv, int span) {
     return (long long)n_tokens * rv_paged_attention_mixed_splits(span) * (2ll * H + (long long)H * dv) * 4;
+}
+
+// The merge alone, for partial results that the tensor-core kernel left: tokens
+// [first_token, first_token + n_tokens), `n_splits` stretches of `stretch` positions each at
+// most, tiles of `tile` query tokens.
+extern "C" int rv_paged_attention_mixed_merge(
+    const float* scratch, int n_splits, const void* rows, int dtype, int row_stride, int gate_off,
+    const int* q_start, const int* ctx_lens, const int* token_req, void* out, int first_token,
+    int n_tokens, int H, int dv, int window, int chunk, const float* sinks, int stretch, int tile,
+    void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (!scratch || n_splits <= 0 || stretch <= 0 || tile <= 0) RV_FAIL("paged_attention_mixed_merge: bad sizes");
+    RV_DISPATCH_DTYPE(dtype, "paged_attention_mixed_merge",
+                      (rv_launch(paged_attention_mixed_merge_kernel<T>, dim3(n_tokens), dim3(256), 0,
+                                 (cudaStream_t)stream, scratch, n_splits, (const T*)rows, row_stride,
+                                 gate_off, q_start, ctx_lens, token_req, (T*)out, first_token, H, dv,
+                                 window, chunk, sinks, stretch, tile)));
+    RV_CHECK_LAUNCH("paged_attention_mixed_merge");
+    return 0;
 }
 
 extern "C" int rv_paged_attention_mixed(
@@ -409,7 +465,7 @@ extern "C" int rv_paged_attention_mixed(
                       page_size, scale, window, chunk, mix, scratch, n_splits);
             rv_launch(paged_attention_mixed_merge_kernel<T>, dim3(n_tokens), dim3(256), 0, s,
                       (const float*)scratch, n_splits, (const T*)rows, row_stride, gate_off, q_start,
-                      ctx_lens, token_req, (T*)out, first_token, H, dv, window, chunk, sinks);
+                      ctx_lens, token_req, (T*)out, first_token, H, dv, window, chunk, sinks, AM_SPLIT, 1);
         });
         RV_CHECK_LAUNCH("paged_attention_mixed");
         return 0;

@@ -8,16 +8,21 @@
 //      the next tile's keys are requested as soon as this tile's scores are formed and its
 //      values as soon as this tile's are used, so both travel behind the arithmetic;
 //   2. warp w forms the raw scores of heads 2w, 2w+1: S_g = scale * Q_g K^T (mma.sync m16n8k16,
-//      float32 accumulators; the Q fragments stay in registers for the whole block) -> shared
-//      memory, float32;
+//      float32 accumulators; the block's query rows stay in shared memory) -> shared memory,
+//      float32;
 //   3. mixing, mask and running softmax in float32 on the CUDA cores: a thread owns 4
 //      neighbouring keys of one query token for 8 heads, s'_h = sum_g M[h, g] s_g as 32 FMAs per
 //      three 16-byte shared-memory loads, maxima and sums over a row by shuffles among the 8
-//      lanes that share the token; P goes to shared memory as bfloat16 (the row sum adds the
-//      rounded values);
+//      lanes that share the token; once every thread has read its scores, P takes their place
+//      in shared memory as bfloat16 (the row sum adds the rounded values);
 //   4. warp w rescales and extends O_h += P_h V of its two heads (V by ldmatrix.trans).
 // The sink enters as the initial maximum with a sum of 1.  The epilogue divides by the sum,
 // multiplies by sigmoid(gate) and writes bfloat16.
+// A launch with too few blocks for the GPU (one prompt of a few thousand tokens: the last blocks
+// of a prompt walk twice the average number of tiles) shares every block's keys out over several
+// blocks, one per stretch of positions aligned to absolute position 0; they leave maxima, sums
+// and unnormalised values in a scratch buffer, and the merge kernel of attention_mixed.cu puts a
+// token's stretches together in order, adds the sink once, divides and gates.
 // Work per (query, key) pair: 2 H (d + dv) tensor-core FLOPs and 2 H^2 float32 FLOPs for the
 // mixing, which the tensor cores cannot take in float32; from 16 heads on the mixing is the
 // longer part.
@@ -59,6 +64,11 @@ __device__ __forceinline__ void am_ldmatrix_x4_trans(unsigned (&r)[4], const voi
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
+__device__ __forceinline__ void am_ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
 __device__ __forceinline__ void am_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
@@ -75,7 +85,8 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
                            const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
                            bf16* __restrict__ out, int first_req, int H, int G, int page_size,
                            float scale, int window, int chunk, const float* __restrict__ mix,
-                           const float* __restrict__ sinks) {
+                           const float* __restrict__ sinks, float* __restrict__ scratch, int stretch,
+                           int first_token) {
     constexpr int D = RV_D, DV = RV_DV;
     rv_pdl_launch_dependents();
     const int r = first_req + blockIdx.y;
@@ -88,8 +99,10 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
     bf16* Ks = (bf16*)smem_raw;                              // [KT][KS]
     bf16* Vs = Ks + AM_KT * KS;                              // [KT][VS]
     float* S = (float*)(Vs + AM_KT * VS);                    // [H][QT][SS]
-    bf16* P = (bf16*)(S + (size_t)H * AM_QT * AM_SS);        // [H][QT][PS]
-    float* Tt = (float*)(P + (size_t)H * AM_QT * AM_PS);     // [H][H]: Tt[g][h] = mix[h][g]
+    bf16* P = (bf16*)S;                                      // [H][QT][PS]: takes S's place once every score is read
+    const int QS = H * D + 8;
+    bf16* Qs = (bf16*)(S + (size_t)H * AM_QT * AM_SS);       // [QT][QS]
+    float* Tt = (float*)(Qs + AM_QT * QS);                   // [H][H]: Tt[g][h] = mix[h][g]
     float* alpha_s = Tt + H * H;                             // [H][QT]
     float* l_s = alpha_s + H * AM_QT;                        // [H][QT] running sums
     float* m_s = l_s + H * AM_QT;                            // [H][QT] running maxima
@@ -113,34 +126,30 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
     if (kg == 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            m_s[(hb * 8 + j) * AM_QT + mq] = sinks ? sinks[hb * 8 + j] : -INFINITY;
-            l_s[(hb * 8 + j) * AM_QT + mq] = sinks ? 1.f : 0.f;
+            m_s[(hb * 8 + j) * AM_QT + mq] = (sinks && !scratch) ? sinks[hb * 8 + j] : -INFINITY;
+            l_s[(hb * 8 + j) * AM_QT + mq] = (sinks && !scratch) ? 1.f : 0.f;
         }
     }
     int lo_first = 0;                                        // lowest key any query of the block sees
     if (window > 0) lo_first = max(lo_first, p_first - window + 1);
     if (chunk > 0) lo_first = max(lo_first, p_first / chunk * chunk);
-    const int p_last = p_first + n_q - 1;
+    int p_last = p_first + n_q - 1;
+    if (scratch) {
+        // a launch that shares a block's keys out: this block takes the blockIdx.z-th stretch of
+        // `stretch` positions (aligned to absolute position 0) that its queries can see
+        const int s_abs = lo_first / stretch + blockIdx.z;
+        if (s_abs * stretch > p_last) return;
+        lo_first = max(lo_first, s_abs * stretch);
+        p_last = min(p_last, (s_abs + 1) * stretch - 1);
+    }
     const int* table = block_table + (size_t)r * max_blocks;
     rv_pdl_wait();
 
-    // Q fragments of this warp's two heads
-    unsigned qf[2][D / 16][4];
-    {
-        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            const int h = 2 * warp + hh;
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-                const bf16* base = rows + (size_t)(q0 + t_first) * row_stride + (size_t)h * D + ks * 16 + c0;
-                const unsigned z = 0u;
-                qf[hh][ks][0] = r0 < n_q ? *(const unsigned*)(base + (size_t)r0 * row_stride) : z;
-                qf[hh][ks][1] = r0 + 8 < n_q ? *(const unsigned*)(base + (size_t)(r0 + 8) * row_stride) : z;
-                qf[hh][ks][2] = r0 < n_q ? *(const unsigned*)(base + (size_t)r0 * row_stride + 8) : z;
-                qf[hh][ks][3] = r0 + 8 < n_q ? *(const unsigned*)(base + (size_t)(r0 + 8) * row_stride + 8) : z;
-            }
-        }
+    // the block's query rows (zeros beyond its last token)
+    for (int i = tid; i < AM_QT * (H * D / 2); i += blockDim.x) {
+        const int row = i / (H * D / 2), c = i - row * (H * D / 2);
+        ((unsigned*)(Qs + row * QS))[c] =
+            row < n_q ? ((const unsigned*)(rows + (size_t)(q0 + t_first + row) * row_stride))[c] : 0u;
     }
     float o[2][DV / 8][4];
 #pragma unroll
@@ -183,13 +192,17 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
         for (int hh = 0; hh < 2; ++hh) {
             const int h = 2 * warp + hh, g = h / hpg;
             float* Sh = S + (size_t)h * AM_QT * AM_SS;
+            unsigned qf[D / 16][4];
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks)
+                am_ldmatrix_x4(qf[ks], Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * QS + h * D + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
             for (int nt = 0; nt < AM_KT / 8; ++nt) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
                 const bf16* kb = Ks + (nt * 8 + (lane >> 2)) * KS + g * D + (lane & 3) * 2;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
-                    am_mma(c, qf[hh][ks], *(const unsigned*)(kb + ks * 16), *(const unsigned*)(kb + ks * 16 + 8));
+                    am_mma(c, qf[ks], *(const unsigned*)(kb + ks * 16), *(const unsigned*)(kb + ks * 16 + 8));
                 const int col = nt * 8 + (lane & 3) * 2;
                 *(float2*)(Sh + (lane >> 2) * AM_SS + col) = make_float2(c[0] * scale, c[1] * scale);
                 *(float2*)(Sh + ((lane >> 2) + 8) * AM_SS + col) = make_float2(c[2] * scale, c[3] * scale);
@@ -197,9 +210,11 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
         }
         __syncthreads();
         load_tile(j0 + AM_KT, true);          // the next tile's keys travel during the mixing
-        // 3. mixing, mask, running softmax
-        {
-            float acc[8][4];
+        // 3. mixing, mask, running softmax; token rows beyond the block's last token do nothing
+        //    (the 8 lanes that share a token leave together, so the shuffles name only them)
+        float acc[8][4];
+        if (mq_live) {
+            const unsigned gmask = 0xFFu << (lane & 24);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -229,12 +244,12 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
                 float mx = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) mx = fmaxf(mx, see[i] ? acc[j][i] : -INFINITY);
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 2));
+                mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 4));
                 const int h = hb * 8 + j;
                 const float m_old = m_s[h * AM_QT + mq], l_old = l_s[h * AM_QT + mq];
-                __syncwarp();
+                __syncwarp(gmask);
                 const float m_new = fmaxf(m_old, mx);
                 float e[4];
                 float sum = 0.f;
@@ -244,21 +259,31 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
                     e[i] = __bfloat162float(__float2bfloat16_rn(e[i]));
                     sum += e[i];
                 }
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                sum += __shfl_xor_sync(gmask, sum, 1);
+                sum += __shfl_xor_sync(gmask, sum, 2);
+                sum += __shfl_xor_sync(gmask, sum, 4);
                 const float alpha = (m_old == -INFINITY) ? (m_new == -INFINITY ? 1.f : 0.f)
                                                          : expf(m_old - m_new);
-                const __nv_bfloat162 p01 = __floats2bfloat162_rn(e[0], e[1]), p23 = __floats2bfloat162_rn(e[2], e[3]);
-                uint2 pk;
-                pk.x = *(const unsigned*)&p01;
-                pk.y = *(const unsigned*)&p23;
-                *(uint2*)(P + ((size_t)h * AM_QT + mq) * AM_PS + kg * 4) = pk;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[j][i] = e[i];
                 if (kg == 0) {
                     alpha_s[h * AM_QT + mq] = alpha;
                     m_s[h * AM_QT + mq] = m_new;
                     l_s[h * AM_QT + mq] = l_old * alpha + sum;
                 }
+            }
+        }
+        __syncthreads();
+        // every score has been read: the probabilities take their place
+        if (mq_live) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const __nv_bfloat162 p01 = __floats2bfloat162_rn(acc[j][0], acc[j][1]);
+                const __nv_bfloat162 p23 = __floats2bfloat162_rn(acc[j][2], acc[j][3]);
+                uint2 pk;
+                pk.x = *(const unsigned*)&p01;
+                pk.y = *(const unsigned*)&p23;
+                *(uint2*)(P + ((size_t)(hb * 8 + j) * AM_QT + mq) * AM_PS + kg * 4) = pk;
             }
         }
         asm volatile("cp.async.wait_group 1;\n" ::);      // this tile's values have landed
@@ -298,6 +323,32 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
     }
     asm volatile("cp.async.wait_group 0;\n" ::);
     const int n_out = H * DV;
+    if (scratch) {
+        // [token][stretch]: H maxima, H sums, H * DV unnormalised values; the merge kernel of
+        // attention_mixed.cu puts a token's stretches together
+        const size_t stride = (size_t)(2 * H + n_out);
+        for (int i = tid; i < H * n_q; i += blockDim.x) {
+            const int h = i / n_q, row = i - h * n_q;
+            float* part = scratch + ((size_t)(q0 + t_first + row - first_token) * gridDim.z + blockIdx.z) * stride;
+            part[h] = m_s[h * AM_QT + row];
+            part[H + h] = l_s[h * AM_QT + row];
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int h = 2 * warp + hh;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = (lane >> 2) + 8 * half;
+                if (row >= n_q) continue;
+                float* part = scratch + ((size_t)(q0 + t_first + row - first_token) * gridDim.z + blockIdx.z) * stride + 2 * H;
+#pragma unroll
+                for (int nt = 0; nt < DV / 8; ++nt)
+                    *(float2*)(part + h * DV + nt * 8 + (lane & 3) * 2) =
+                        make_float2(o[hh][nt][2 * half], o[hh][nt][2 * half + 1]);
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const int h = 2 * warp + hh;
@@ -325,7 +376,7 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
 
 extern "C" long long AM_NAME(rv_attention_mixed_mma_smem_d)(int H, int G) {
     return (long long)AM_KT * (G * RV_D + 8) * 2 + (long long)AM_KT * (G * RV_DV + 8) * 2 +
-           (long long)H * AM_QT * AM_SS * 4 + (long long)H * AM_QT * AM_PS * 2 + (long long)H * H * 4 +
+           (long long)H * AM_QT * AM_SS * 4 + (long long)AM_QT * (H * RV_D + 8) * 2 + (long long)H * H * 4 +
            3ll * H * AM_QT * 4;
 }
 
@@ -334,7 +385,11 @@ extern "C" int AM_NAME(rv_attention_mixed_mma_d)(
     const void* rows, int row_stride, int gate_off, const void* k_cache, const void* v_cache,
     const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens, void* out,
     int first_req, int n_reqs, int max_q_len, int H, int G, int page_size, float scale, int window,
-    int chunk, const float* mix, const float* sinks, void* stream) {
+    int chunk, const float* mix, const float* sinks, float* scratch, int stretch, int n_stretch,
+    int first_token, void* stream) {
+    // `scratch` given: every block's keys are shared out over up to `n_stretch` blocks, one per
+    // `stretch` positions, which leave partial results there for the merge kernel; it holds
+    // (tokens from `first_token` on) * n_stretch * (2 H + H dv) floats
     if (n_reqs <= 0 || max_q_len <= 0) return 0;
     if (H <= 0 || H % 8 || H > 32 || G <= 0 || H % G) AM_FAIL("attention_mixed_mma: %d heads (multiples of 8 up to 32) over %d key/value heads", H, G);
     if (row_stride % 2 || (gate_off >= 0 && gate_off % 2) || ((uintptr_t)rows % 4) || ((uintptr_t)out % 4) ||
@@ -351,10 +406,12 @@ extern "C" int AM_NAME(rv_attention_mixed_mma_d)(
         if (e != cudaSuccess) AM_FAIL("attention_mixed_mma: %s", cudaGetErrorString(e));
         configured[H > 16] = smem;
     }
-    rv_launch(kernel, dim3((max_q_len + AM_QT - 1) / AM_QT, n_reqs), dim3(16 * H),
+    if (scratch && (stretch <= 0 || stretch % AM_KT || n_stretch <= 0)) AM_FAIL("attention_mixed_mma: bad stretch");
+    rv_launch(kernel, dim3((max_q_len + AM_QT - 1) / AM_QT, n_reqs, scratch ? n_stretch : 1), dim3(16 * H),
               (size_t)smem, (cudaStream_t)stream, (const bf16*)rows, row_stride, gate_off,
               (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, q_start, ctx_lens,
-              (bf16*)out, first_req, H, G, page_size, scale, window, chunk, mix, sinks);
+              (bf16*)out, first_req, H, G, page_size, scale, window, chunk, mix, sinks, scratch,
+              stretch, first_token);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) AM_FAIL("attention_mixed_mma: %s", cudaGetErrorString(e));
     return 0;

@@ -699,6 +699,8 @@ class CudaOps:
         if out.shape[1] != num_heads * v_head_dim:
             raise KernelError("paged_attention_mixed: output width and head sizes disagree")
         nd = ctx.n_decode
+        # (the tensor-core kernel would take single tokens as portions of one token, but fifteen
+        # of a tile's sixteen rows are then idle; measured slower than the split kernel)
         tensor = ctx.n_tokens > nd and self._mixed_mma_ok(rows, num_heads, num_kv_heads, head_dim,
                                                           v_head_dim, gate_off)
         # single tokens, and everything the tensor-core kernel does not take: one block a token
@@ -730,17 +732,44 @@ class CudaOps:
         if tensor:
             lib = self._mixed_lib(head_dim, v_head_dim)
             tag = f"{head_dim}_{v_head_dim}"
+            # too few blocks for the GPU (a block is 16 tokens): every block's keys are shared out
+            # over `parts` blocks, one per stretch of positions, and a merge puts them together
+            n_prompt = ctx.n_tokens - nd
+            tiles = -(-n_prompt // 16)
+            parts = min(16, -(-3 * self._sm_count // max(1, tiles)))
+            scratch, stretch, n_stretch = None, 0, 0
+            if parts >= 2 and os.environ.get("RVLLM_MIXED_SHARE", "1") != "0":
+                span = self._mixed_span(ctx.max_ctx_len, window, chunk) + 15
+                stretch = max(128, -(-(-(-span // parts)) // 32) * 32)
+                n_stretch = -(-span // stretch) + 1
+                need = n_prompt * n_stretch * (2 * num_heads + num_heads * v_head_dim) * 4
+                have = self._scratch.get(str(rows.device))
+                if n_stretch < 2:
+                    pass
+                elif have is not None and have.numel() >= need:
+                    scratch = have
+                elif not torch.cuda.is_current_stream_capturing():
+                    scratch = self._scratch_buffer(need, rows.device)
             rc = getattr(lib, f"rv_attention_mixed_mma_d{tag}")(
                 _ptr(rows), c_int(rows.shape[1]), c_int(gate_off), _ptr(k_cache), _ptr(v_cache),
                 _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
                 _ptr(ctx.ctx_lens), _ptr(out), c_int(nd), c_int(ctx.n_reqs - nd),
                 c_int(ctx.max_q_len), c_int(num_heads), c_int(num_kv_heads),
                 c_int(group.page_size), c_float(scale), c_int(window if window else 0),
-                c_int(chunk if chunk else 0), _ptr(head_mix), _ptr(sinks), self._stream())
+                c_int(chunk if chunk else 0), _ptr(head_mix), _ptr(sinks), _ptr(scratch),
+                c_int(stretch), c_int(n_stretch), c_int(nd), self._stream())
             self.launches += 1
             if rc != 0:
                 msg = getattr(lib, f"rv_attention_mixed_mma_last_error_d{tag}")().decode()
                 raise KernelError(f"paged_attention_mixed: {msg}")
+            if scratch is not None:
+                self._check(self.lib.rv_paged_attention_mixed_merge(
+                    _ptr(scratch), c_int(n_stretch), _ptr(rows), _code(rows.dtype),
+                    c_int(rows.shape[1]), c_int(gate_off), _ptr(ctx.q_start), _ptr(ctx.ctx_lens),
+                    _ptr(ctx.token_req), _ptr(out), c_int(nd), c_int(n_prompt), c_int(num_heads),
+                    c_int(v_head_dim), c_int(window if window else 0), c_int(chunk if chunk else 0),
+                    _ptr(sinks), c_int(stretch), c_int(16), self._stream()),
+                    "paged_attention_mixed_merge")
 
     @staticmethod
     def _mixed_span(max_ctx_len, window, chunk) -> int:
@@ -770,7 +799,8 @@ class CudaOps:
         if rows.shape[1] % 2 or (gate_off >= 0 and gate_off % 2):
             return False
         smem = 32 * (num_kv_heads * (head_dim + v_head_dim) + 16) * 2 \
-            + num_heads * 16 * 40 * 6 + num_heads * num_heads * 4 + num_heads * 192
+            + num_heads * 16 * 40 * 4 + 16 * (num_heads * head_dim + 8) * 2 \
+            + num_heads * num_heads * 4 + num_heads * 192
         return smem <= 227 * 1024
 
     def _mixed_lib(self, head_dim: int, v_head_dim: int):
