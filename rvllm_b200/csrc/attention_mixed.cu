@@ -170,9 +170,13 @@ __global__ void paged_attention_mixed_kernel(
 
 // Single tokens, split over the keys.  Block (token, s) stages tiles of 32 keys and values of
 // its stretch in shared memory (rows padded to an odd number of 32-bit words, so that a warp
-// whose lanes walk 32 keys meets no bank twice), forms the raw scores with a thread per (head,
-// key), mixes, keeps a running maximum and sum per head, and accumulates the values with a
-// thread per output element.
+// whose lanes walk 32 keys meets no bank twice).  Raw scores: a warp per key/value head, a lane
+// per key, the key's values read once for up to four query heads of the group.  Mixing: a thread
+// per (four heads, key) with the mixing matrix transposed, so that one score meets four
+// coefficients in one 16-byte load.  Running maximum and sum: a warp per head.  Values: a thread
+// per (four heads, two neighbouring value dimensions), probabilities transposed to [key][head].
+#define AM_SPLIT_ITEMS 2      // (four heads x two dimensions) items a thread: H * dv <= 4096
+
 template <typename T>
 __global__ void paged_attention_mixed_split_kernel(
     const T* __restrict__ rows, int row_stride, const T* __restrict__ k_cache,
@@ -183,16 +187,18 @@ __global__ void paged_attention_mixed_split_kernel(
     float* __restrict__ scratch, int n_splits) {
     rv_pdl_launch_dependents();
     constexpr int PER = 4 / sizeof(T);                 // elements per 32-bit word
-    const int kw = G * d / PER + 1, vw = G * dv / PER + 1;          // row lengths in words (odd: G*d, G*dv are multiples of 2*PER)
-    extern __shared__ float smem[];
-    float* q_s = smem;                                 // [H * d]
-    float* mix_s = q_s + H * d;                        // [H * H]
-    float* raw_s = mix_s + H * H;                      // [H][KT + 1]
-    float* p_s = raw_s + H * (AM_KT + 1);              // [H][KT + 1]
+    const int kw = G * d / PER + 1, vw = G * dv / PER + 1;          // row lengths in words (odd)
+    const int HP = (H + 3) & ~3, HPP = HP + 4;
+    extern __shared__ __align__(16) float smem[];
+    float* mixT = smem;                                // [H][HP]: mixT[g][h] = mix[h][g]
+    float* p_t = mixT + H * HP;                        // [KT][HPP] probabilities, transposed
+    float* q_s = p_t + AM_KT * HPP;                    // [H * d]
+    float* raw_s = q_s + ((H * d + 3) & ~3);           // [H][KT + 1]
+    float* p_s = raw_s + H * (AM_KT + 1);              // [H][KT + 1] mixed scores
     float* m_s = p_s + H * (AM_KT + 1);                // [H]
     float* l_s = m_s + H;
-    float* alpha_s = l_s + H;
-    unsigned* kt = (unsigned*)(alpha_s + H);           // [KT][kw] words
+    float* alpha_s = l_s + H;                          // [HP]
+    unsigned* kt = (unsigned*)(alpha_s + HP);          // [KT][kw] words
     unsigned* vt = kt + AM_KT * kw;                    // [KT][vw] words
     __shared__ long long slot_s[AM_KT];
     const int t = first_token + blockIdx.x;
@@ -208,20 +214,30 @@ __global__ void paged_attention_mixed_split_kernel(
     if (s_abs * AM_SPLIT > p) return;                          // the token has fewer stretches
     lo = max(lo, s_abs * AM_SPLIT);
     const int hi = min(p, (s_abs + 1) * AM_SPLIT - 1);
-    if (mix)
-        for (int i = tid; i < H * H; i += blockDim.x) mix_s[i] = mix[i];
-    for (int h = tid; h < H; h += blockDim.x) {
-        m_s[h] = -INFINITY;
-        l_s[h] = 0.f;
+    for (int i = tid; i < H * HP; i += blockDim.x) {
+        const int g = i / HP, h = i - g * HP;
+        mixT[i] = h < H ? (mix ? mix[h * H + g] : (g == h ? 1.f : 0.f)) : 0.f;
     }
+    for (int h = tid; h < HP; h += blockDim.x) {
+        if (h < H) {
+            m_s[h] = -INFINITY;
+            l_s[h] = 0.f;
+        }
+        alpha_s[h] = 0.f;
+    }
+    for (int i = tid; i < AM_KT * HPP; i += blockDim.x) p_t[i] = 0.f;
     rv_pdl_wait();
     const T* row = rows + (size_t)t * row_stride;
     for (int i = tid; i < H * d; i += blockDim.x) q_s[i] = rv_load(row + i);
     const int hpg = H / G;
     const int n_out = H * dv;
-    float acc[AM_MAX_ACC];
+    const bool one_group = hpg % 4 == 0;                       // four neighbouring heads share their values
+    const int n_items = (HP / 4) * (dv / 2);
+    float acc[AM_SPLIT_ITEMS][8];
 #pragma unroll
-    for (int i = 0; i < AM_MAX_ACC; ++i) acc[i] = 0.f;
+    for (int i = 0; i < AM_SPLIT_ITEMS; ++i)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[i][u] = 0.f;
     const int* table = block_table + (size_t)r * max_blocks;
     const int krow = G * d / PER, vrow = G * dv / PER;         // words of a key / value row
     const bool vec16 = krow % 4 == 0 && vrow % 4 == 0 && (uintptr_t)k_cache % 16 == 0 &&
@@ -239,76 +255,89 @@ __global__ void paged_attention_mixed_split_kernel(
         }
         __syncthreads();
         if (vec16) {
-            // 16-byte loads, four in flight per thread before any is stored
-            const int kq = krow / 4, vq = vrow / 4, per = kq + vq, total = AM_KT * per;
-            for (int base = tid; base < total; base += 4 * blockDim.x) {
-                uint4 val[4];
+            // a warp per key: 16-byte loads, up to four in flight per lane before any is stored
+            const int kq = krow / 4, per = kq + vrow / 4;
+            for (int jj = warp; jj < AM_KT; jj += nwarps) {
+                const long long s = slot_s[jj];
+                const uint4* ksrc = (const uint4*)k_cache + (size_t)(s < 0 ? 0 : s) * kq;
+                const uint4* vsrc = (const uint4*)v_cache + (size_t)(s < 0 ? 0 : s) * (per - kq);
+                for (int c0 = lane; c0 < per; c0 += 128) {
+                    uint4 val[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int i = base + u * blockDim.x;
-                    val[u] = make_uint4(0u, 0u, 0u, 0u);
-                    if (i < total) {
-                        const int jj = i / per, c = i - jj * per;
-                        const long long s = slot_s[jj];
-                        if (s >= 0)
-                            val[u] = c < kq ? ((const uint4*)k_cache)[(size_t)s * kq + c]
-                                            : ((const uint4*)v_cache)[(size_t)s * vq + c - kq];
+                    for (int u = 0; u < 4; ++u) {
+                        const int c = c0 + 32 * u;
+                        val[u] = make_uint4(0u, 0u, 0u, 0u);
+                        if (c < per && s >= 0) val[u] = c < kq ? ksrc[c] : vsrc[c - kq];
                     }
-                }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int i = base + u * blockDim.x;
-                    if (i < total) {
-                        const int jj = i / per, c = i - jj * per;
-                        unsigned* dst = c < kq ? kt + jj * kw + 4 * c : vt + jj * vw + 4 * (c - kq);
-                        dst[0] = val[u].x; dst[1] = val[u].y; dst[2] = val[u].z; dst[3] = val[u].w;
+                    for (int u = 0; u < 4; ++u) {
+                        const int c = c0 + 32 * u;
+                        if (c < per) {
+                            unsigned* dst = c < kq ? kt + jj * kw + 4 * c : vt + jj * vw + 4 * (c - kq);
+                            dst[0] = val[u].x; dst[1] = val[u].y; dst[2] = val[u].z; dst[3] = val[u].w;
+                        }
                     }
                 }
             }
         } else {
-            for (int i = tid; i < AM_KT * (krow + vrow); i += blockDim.x) {
-                const int jj = i / (krow + vrow), c = i - jj * (krow + vrow);
+            for (int jj = warp; jj < AM_KT; jj += nwarps) {
                 const long long s = slot_s[jj];
-                if (c < krow)
+                for (int c = lane; c < krow; c += 32)
                     kt[jj * kw + c] = s < 0 ? 0u : ((const unsigned*)k_cache)[(size_t)s * krow + c];
-                else
-                    vt[jj * vw + c - krow] = s < 0 ? 0u : ((const unsigned*)v_cache)[(size_t)s * vrow + c - krow];
+                for (int c = lane; c < vrow; c += 32)
+                    vt[jj * vw + c] = s < 0 ? 0u : ((const unsigned*)v_cache)[(size_t)s * vrow + c];
             }
         }
         __syncthreads();
-        // raw scores: a warp per head, a lane per key
-        for (int h = warp; h < H; h += nwarps) {
-            const int g = h / hpg;
+        // raw scores: a warp per key/value head, a lane per key, four query heads at a time
+        for (int g = warp; g < G; g += nwarps) {
             const T* kr = (const T*)(kt + lane * kw) + g * d;
-            const float* qh = q_s + h * d;
-            float dot = 0.f;
-            for (int i = 0; i < d; i += 2) {
-                float k0, k1;
-                if (sizeof(T) == 2) {
-                    const float2 kk = __bfloat1622float2(*(const __nv_bfloat162*)(kr + i));
-                    k0 = kk.x;
-                    k1 = kk.y;
-                } else {
-                    k0 = rv_load(kr + i);
-                    k1 = rv_load(kr + i + 1);
+            for (int hh0 = 0; hh0 < hpg; hh0 += 4) {
+                float dot[4] = {0.f, 0.f, 0.f, 0.f};
+                const int nh = min(4, hpg - hh0);
+                const float* qh = q_s + (size_t)(g * hpg + hh0) * d;
+                // heads beyond the group read the group's last head again; their sums are dropped
+                const float* q0 = qh, *q1 = qh + min(1, nh - 1) * d, *q2 = qh + min(2, nh - 1) * d,
+                           *q3 = qh + min(3, nh - 1) * d;
+#pragma unroll 4
+                for (int i = 0; i < d; i += 2) {
+                    float k0, k1;
+                    if (sizeof(T) == 2) {
+                        const float2 kk = __bfloat1622float2(*(const __nv_bfloat162*)(kr + i));
+                        k0 = kk.x;
+                        k1 = kk.y;
+                    } else {
+                        k0 = rv_load(kr + i);
+                        k1 = rv_load(kr + i + 1);
+                    }
+                    const float2 a0 = *(const float2*)(q0 + i), a1 = *(const float2*)(q1 + i),
+                                 a2 = *(const float2*)(q2 + i), a3 = *(const float2*)(q3 + i);
+                    dot[0] += a0.x * k0 + a0.y * k1;
+                    dot[1] += a1.x * k0 + a1.y * k1;
+                    dot[2] += a2.x * k0 + a2.y * k1;
+                    dot[3] += a3.x * k0 + a3.y * k1;
                 }
-                dot += qh[i] * k0 + qh[i + 1] * k1;
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (u < nh) raw_s[(g * hpg + hh0 + u) * (AM_KT + 1) + lane] = dot[u] * scale;
             }
-            raw_s[h * (AM_KT + 1) + lane] = dot * scale;
         }
         __syncthreads();
-        for (int i = tid; i < H * AM_KT; i += blockDim.x) {
-            const int h = i / AM_KT, jj = i - h * AM_KT;
-            float v = -INFINITY;
-            if (slot_s[jj] >= 0) {
-                if (mix) {
-                    v = 0.f;
-                    for (int g = 0; g < H; ++g) v += mix_s[h * H + g] * raw_s[g * (AM_KT + 1) + jj];
-                } else {
-                    v = raw_s[h * (AM_KT + 1) + jj];
+        // mixing over the heads, and the mask: a thread per (four heads, key)
+        for (int i = tid; i < (HP / 4) * AM_KT; i += blockDim.x) {
+            const int hq = i / AM_KT, jj = i - hq * AM_KT;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            const bool seen = slot_s[jj] >= 0;
+            if (seen)
+#pragma unroll 8
+                for (int g = 0; g < H; ++g) {
+                    const float rw = raw_s[g * (AM_KT + 1) + jj];
+                    const float4 m4 = *(const float4*)(mixT + g * HP + hq * 4);
+                    v[0] += m4.x * rw; v[1] += m4.y * rw; v[2] += m4.z * rw; v[3] += m4.w * rw;
                 }
-            }
-            p_s[h * (AM_KT + 1) + jj] = v;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (hq * 4 + u < H) p_s[(hq * 4 + u) * (AM_KT + 1) + jj] = seen ? v[u] : -INFINITY;
         }
         __syncthreads();
         for (int h = warp; h < H; h += nwarps) {
@@ -318,7 +347,7 @@ __global__ void paged_attention_mixed_split_kernel(
             const float e = (v == -INFINITY) ? 0.f : expf(v - m_new);
             const float sum = rv_warp_sum(e);
             const float alpha = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
-            p_s[h * (AM_KT + 1) + lane] = e;
+            p_t[lane * HPP + h] = e;
             if (lane == 0) {
                 m_s[h] = m_new;
                 l_s[h] = l_s[h] * alpha + sum;
@@ -326,16 +355,48 @@ __global__ void paged_attention_mixed_split_kernel(
             }
         }
         __syncthreads();
+        // values: a thread per (four heads, two neighbouring dimensions)
 #pragma unroll
-        for (int i = 0; i < AM_MAX_ACC; ++i) {
-            const int e = tid + i * AM_THREADS;
-            if (e < n_out) {
-                const int h = e / dv, dd = e - h * dv, g = h / hpg;
-                float a = acc[i] * alpha_s[h];
-                const float* ph = p_s + h * (AM_KT + 1);
-                const T* vcol = (const T*)vt + g * dv + dd;
-                for (int jj = 0; jj < AM_KT; ++jj) a += ph[jj] * rv_load(vcol + (size_t)jj * vw * PER);
-                acc[i] = a;
+        for (int it = 0; it < AM_SPLIT_ITEMS; ++it) {
+            const int item = tid + it * AM_THREADS;
+            if (item < n_items) {
+                const int hq = item / (dv / 2), dd = (item - hq * (dv / 2)) * 2;
+                const float4 al = *(const float4*)(alpha_s + hq * 4);
+                acc[it][0] *= al.x; acc[it][1] *= al.x; acc[it][2] *= al.y; acc[it][3] *= al.y;
+                acc[it][4] *= al.z; acc[it][5] *= al.z; acc[it][6] *= al.w; acc[it][7] *= al.w;
+                if (one_group) {
+                    const T* vcol = (const T*)vt + (hq * 4 / hpg) * dv + dd;
+#pragma unroll 8
+                    for (int jj = 0; jj < AM_KT; ++jj) {
+                        const float4 pr = *(const float4*)(p_t + jj * HPP + hq * 4);
+                        const T* vp = vcol + (size_t)jj * vw * PER;
+                        float v0, v1;
+                        if (sizeof(T) == 2) {
+                            const float2 vv = __bfloat1622float2(*(const __nv_bfloat162*)vp);
+                            v0 = vv.x;
+                            v1 = vv.y;
+                        } else {
+                            v0 = rv_load(vp);
+                            v1 = rv_load(vp + 1);
+                        }
+                        acc[it][0] += pr.x * v0; acc[it][1] += pr.x * v1;
+                        acc[it][2] += pr.y * v0; acc[it][3] += pr.y * v1;
+                        acc[it][4] += pr.z * v0; acc[it][5] += pr.z * v1;
+                        acc[it][6] += pr.w * v0; acc[it][7] += pr.w * v1;
+                    }
+                } else {
+                    for (int jj = 0; jj < AM_KT; ++jj) {
+                        const float4 pr = *(const float4*)(p_t + jj * HPP + hq * 4);
+                        const float pu[4] = {pr.x, pr.y, pr.z, pr.w};
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int h = min(hq * 4 + u, H - 1);
+                            const T* vp = (const T*)vt + (size_t)jj * vw * PER + (h / hpg) * dv + dd;
+                            acc[it][2 * u] += pu[u] * rv_load(vp);
+                            acc[it][2 * u + 1] += pu[u] * rv_load(vp + 1);
+                        }
+                    }
+                }
             }
         }
     }
@@ -347,9 +408,17 @@ __global__ void paged_attention_mixed_split_kernel(
         part[H + h] = l_s[h];
     }
 #pragma unroll
-    for (int i = 0; i < AM_MAX_ACC; ++i) {
-        const int e = tid + i * AM_THREADS;
-        if (e < n_out) part[2 * H + e] = acc[i];
+    for (int it = 0; it < AM_SPLIT_ITEMS; ++it) {
+        const int item = tid + it * AM_THREADS;
+        if (item < n_items) {
+            const int hq = item / (dv / 2), dd = (item - hq * (dv / 2)) * 2;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (hq * 4 + u < H) {
+                    part[2 * H + (hq * 4 + u) * dv + dd] = acc[it][2 * u];
+                    part[2 * H + (hq * 4 + u) * dv + dd + 1] = acc[it][2 * u + 1];
+                }
+        }
     }
 }
 
@@ -448,9 +517,13 @@ extern "C" int rv_paged_attention_mixed(
         if (rv_paged_attention_mixed_scratch_bytes(n_tokens, H, dv, span) > scratch_bytes)
             RV_FAIL("paged_attention_mixed: the scratch buffer is too small");
         const int el = dtype == RV_DTYPE_BF16 ? 2 : 4;
-        if ((G * d * el) % 8 || (G * dv * el) % 8 || (uintptr_t)k_cache % 4 || (uintptr_t)v_cache % 4 || d % 2)
+        if ((G * d * el) % 8 || (G * dv * el) % 8 || (uintptr_t)k_cache % 4 || (uintptr_t)v_cache % 4 || d % 2 || dv % 2)
             RV_FAIL("paged_attention_mixed: key and value rows of %d and %d bytes cannot be staged", G * d * el, G * dv * el);
-        const size_t ssmem = sizeof(float) * ((size_t)H * d + (size_t)H * H + 2 * (size_t)H * (AM_KT + 1) + 3 * H) +
+        const int HP = (H + 3) & ~3;
+        if ((HP / 4) * (dv / 2) > AM_SPLIT_ITEMS * AM_THREADS)
+            RV_FAIL("paged_attention_mixed: %d heads of %d values exceed the split kernel", H, dv);
+        const size_t ssmem = sizeof(float) * ((size_t)H * HP + (size_t)AM_KT * (HP + 4) + (((size_t)H * d + 3) & ~(size_t)3) +
+                                              2 * (size_t)H * (AM_KT + 1) + 2 * H + HP) +
                              4 * (size_t)AM_KT * ((size_t)G * d * el / 4 + 1 + (size_t)G * dv * el / 4 + 1);
         if (ssmem > 200 * 1024) RV_FAIL("paged_attention_mixed: %d heads of size %d do not fit shared memory", H, d);
         RV_DISPATCH_DTYPE(dtype, "paged_attention_mixed", {

@@ -159,15 +159,16 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[hh][nt][i] = 0.f;
 
-    // keys of tile j0 into Ks / values into Vs: 16-byte pieces, zeros where nothing is seen
+    // keys of tile j0 into Ks / values into Vs: a warp per key, 16-byte pieces, zeros where
+    // nothing is seen
+    const int nwarps = blockDim.x >> 5;
     auto load_tile = [&](int j0, bool keys) {
         const int chunks = (keys ? G * D : G * DV) / 8;
         bf16* dst = keys ? Ks : Vs;
         const bf16* src = keys ? k_cache : v_cache;
         const int stride = keys ? KS : VS;
         if (j0 <= p_last)
-            for (int i = tid; i < AM_KT * chunks; i += blockDim.x) {
-                const int jj = i / chunks, c = i - jj * chunks;
+            for (int jj = warp; jj < AM_KT; jj += nwarps) {
                 const int j = j0 + jj;
                 bool valid = j >= lo_first && j <= p_last;
                 long long slot = 0;
@@ -176,7 +177,8 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
                     valid = page >= 0;
                     slot = (long long)page * page_size + j % page_size;
                 }
-                am_cp_async_16(dst + jj * stride + c * 8, src + ((size_t)slot * chunks + c) * 8, valid);
+                for (int c = lane; c < chunks; c += 32)
+                    am_cp_async_16(dst + jj * stride + c * 8, src + ((size_t)slot * chunks + c) * 8, valid);
             }
         asm volatile("cp.async.commit_group;\n" ::);
     };

@@ -717,8 +717,9 @@ class CudaOps:
 
         el = rows.element_size()
         staged = (num_kv_heads * head_dim * el) % 8 == 0 and (num_kv_heads * v_head_dim * el) % 8 == 0 \
-            and head_dim % 2 == 0 and 4 * (num_heads * (head_dim + num_heads + 70) + 8 * num_kv_heads
-                                           * (head_dim + v_head_dim) * el + 64) <= 200 * 1024
+            and head_dim % 2 == 0 and v_head_dim % 2 == 0 \
+            and 4 * (num_heads * (head_dim + num_heads + 110) + 8 * num_kv_heads
+                     * (head_dim + v_head_dim) * el + 512) <= 200 * 1024
         if nd > 0 and staged:
             # single tokens: each split over the keys it sees, then put together
             span = self._mixed_span(ctx.max_ctx_len, window, chunk)

@@ -73,8 +73,17 @@ RX_D = {
     ],
 }
 
-CONFIGS = {"A": RX_A, "B": RX_B, "C": RX_C, "D": RX_D}
-SEEDS = {"A": 11, "B": 12, "C": 13, "D": 14}
+# sizes that no vector access divides: keys of 10, values of 6, three heads, a width of 50
+RX_E = {
+    "architecture": "Retorax", "vocab": 99, "width": 50, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "mingru", "mixer": {"width": 30}, "mlp": _ff(70)},
+        {"type": "attention", "mixer": _attn(3, 3, 10, 6, 0.3, 2, 10.0, 19), "mlp": _ff(34)},
+    ],
+}
+
+CONFIGS = {"A": RX_A, "B": RX_B, "C": RX_C, "D": RX_D, "E": RX_E}
+SEEDS = {"A": 11, "B": 12, "C": 13, "D": 14, "E": 15}
 
 
 def config(name: str) -> dict:

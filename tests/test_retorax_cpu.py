@@ -92,7 +92,7 @@ def test_pages_of_finished_chunks_come_back():
     assert cache.groups[0].pool.in_use == 0
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
 @pytest.mark.parametrize("schedule", ["whole", "tail_decode", "portions", "mixed"])
 def test_engine_host_side_under_every_cut(folders, name, schedule):
     model, _ = load_model(folders[name], "float32", "cpu", PlainOps())
