@@ -77,8 +77,10 @@ __device__ __forceinline__ void am_mma(float (&c)[4], const unsigned (&a)[4], un
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Up to 16 heads a block has 256 threads and two blocks share an SM (one's products run beside
+// the other's mixing); above, 512 threads and one block.  128 registers either way.
 template <int MAXT>
-__global__ void __launch_bounds__(MAXT)
+__global__ void __launch_bounds__(MAXT, MAXT == 256 ? 2 : 1)
 attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int gate_off,
                            const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                            const int* __restrict__ block_table, int max_blocks,
@@ -399,8 +401,6 @@ extern "C" int AM_NAME(rv_attention_mixed_mma_d)(
         AM_FAIL("attention_mixed_mma: rows or pages are not aligned");
     const long long smem = AM_NAME(rv_attention_mixed_mma_smem_d)(H, G);
     if (smem > 227 * 1024) AM_FAIL("attention_mixed_mma: %lld bytes of shared memory", smem);
-    // up to 16 heads a block has 256 threads and the compiler all the registers it wants; above,
-    // 512 threads of 128 registers
     auto kernel = H <= 16 ? attention_mixed_mma_kernel<256> : attention_mixed_mma_kernel<512>;
     static long long configured[2] = {0, 0};
     if (smem > configured[H > 16]) {

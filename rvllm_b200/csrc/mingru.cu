@@ -19,7 +19,8 @@
 #define RV_MINGRU_CHUNKED_FROM 64
 #define RV_MINGRU_KEEP 16          // chunks up to this many tokens keep their gates in registers
 
-__device__ __forceinline__ float rv_sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
+// 1 / (1 + e^-x); the reciprocal is the correctly rounded one, as the division would give
+__device__ __forceinline__ float rv_sigmoid(float x) { return __frcp_rn(1.f + expf(-x)); }
 
 __device__ __forceinline__ void mingru_gate(float pz, float px, float bz, float bx, float& a,
                                             float& b) {
