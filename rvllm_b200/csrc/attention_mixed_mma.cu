@@ -11,8 +11,9 @@
 //      float32 accumulators; the block's query rows stay in shared memory) -> shared memory,
 //      float32;
 //   3. mixing, mask and running softmax in float32 on the CUDA cores: a thread owns 4
-//      neighbouring keys of one query token for 8 heads, s'_h = sum_g M[h, g] s_g as 32 FMAs per
-//      three 16-byte shared-memory loads, maxima and sums over a row by shuffles among the 8
+//      neighbouring keys of one query token for 8 heads, s'_h = sum_g M[h, g] s_g as 16 packed
+//      multiply-adds (fma.rn.f32x2) per five 16-byte shared-memory loads; scores are kept in
+//      units of log 2, so the exponentials are exp2; maxima and sums over a row by shuffles among the 8
 //      lanes that share the token; once every thread has read its scores, P takes their place
 //      in shared memory as bfloat16 (the row sum adds the rounded values);
 //   4. warp w rescales and extends O_h += P_h V of its two heads (V by ldmatrix.trans).
@@ -37,6 +38,8 @@
 
 #define AM_KT 32
 #define AM_QT 16
+#define AM_LOG2E 1.4426950408889634f
+#define AM_LN2 0.6931471805599453f
 #define AM_SS 40          // float32 score row: 32 + 8 (conflict-free fragment stores)
 #define AM_PS 40          // bfloat16 probability row: 32 + 8
 
@@ -68,6 +71,10 @@ __device__ __forceinline__ void am_ldmatrix_x4(unsigned (&r)[4], const void* sme
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+// two float32 multiply-adds in one instruction: c = a * b + c on both halves
+__device__ __forceinline__ void am_fma2(unsigned long long& c, unsigned long long a, unsigned long long b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c) : "l"(a), "l"(b));
 }
 __device__ __forceinline__ void am_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
     asm volatile(
@@ -104,15 +111,18 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
     bf16* P = (bf16*)S;                                      // [H][QT][PS]: takes S's place once every score is read
     const int QS = H * D + 8;
     bf16* Qs = (bf16*)(S + (size_t)H * AM_QT * AM_SS);       // [QT][QS]
-    float* Tt = (float*)(Qs + AM_QT * QS);                   // [H][H]: Tt[g][h] = mix[h][g]
-    float* alpha_s = Tt + H * H;                             // [H][QT]
+    float* Tt = (float*)(Qs + AM_QT * QS);                   // [H][H][2]: Tt[g][h] = (mix[h][g], mix[h][g])
+    float* alpha_s = Tt + 2 * H * H;                         // [H][QT]
     float* l_s = alpha_s + H * AM_QT;                        // [H][QT] running sums
     float* m_s = l_s + H * AM_QT;                            // [H][QT] running maxima
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hpg = H / G;
+    const float scale2 = scale * AM_LOG2E;                   // scores are kept in units of log 2: exponentials are exp2
     for (int i = tid; i < H * H; i += blockDim.x) {
         const int g = i / H, h = i - g * H;
-        Tt[i] = mix ? mix[h * H + g] : (g == h ? 1.f : 0.f);
+        const float m = mix ? mix[h * H + g] : (g == h ? 1.f : 0.f);
+        Tt[2 * i] = m;                                       // both halves of a packed multiply-add
+        Tt[2 * i + 1] = m;
     }
     const int p_first = clen - q_len + t_first;              // position of the block's first query
     const int n_q = min(AM_QT, q_len - t_first);
@@ -128,7 +138,7 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
     if (kg == 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            m_s[(hb * 8 + j) * AM_QT + mq] = (sinks && !scratch) ? sinks[hb * 8 + j] : -INFINITY;
+            m_s[(hb * 8 + j) * AM_QT + mq] = (sinks && !scratch) ? sinks[hb * 8 + j] * AM_LOG2E : -INFINITY;
             l_s[(hb * 8 + j) * AM_QT + mq] = (sinks && !scratch) ? 1.f : 0.f;
         }
     }
@@ -208,8 +218,8 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
                 for (int ks = 0; ks < D / 16; ++ks)
                     am_mma(c, qf[ks], *(const unsigned*)(kb + ks * 16), *(const unsigned*)(kb + ks * 16 + 8));
                 const int col = nt * 8 + (lane & 3) * 2;
-                *(float2*)(Sh + (lane >> 2) * AM_SS + col) = make_float2(c[0] * scale, c[1] * scale);
-                *(float2*)(Sh + ((lane >> 2) + 8) * AM_SS + col) = make_float2(c[2] * scale, c[3] * scale);
+                *(float2*)(Sh + (lane >> 2) * AM_SS + col) = make_float2(c[0] * scale2, c[1] * scale2);
+                *(float2*)(Sh + ((lane >> 2) + 8) * AM_SS + col) = make_float2(c[2] * scale2, c[3] * scale2);
             }
         }
         __syncthreads();
@@ -219,23 +229,31 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
         float acc[8][4];
         if (mq_live) {
             const unsigned gmask = 0xFFu << (lane & 24);
+            // s'_h = sum_g M[h, g] s_g for 8 heads x 4 keys: packed float32 multiply-adds (two keys
+            // an instruction), the coefficient in both halves
+            unsigned long long acc2[8][2];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+            for (int j = 0; j < 8; ++j) acc2[j][0] = acc2[j][1] = 0ull;
             const float* sp = S + mq * AM_SS + kg * 4;
-            const float* tp = Tt + hb * 8;
+            const float* tp = Tt + hb * 16;
             for (int g = 0; g < H; ++g) {
-                const float4 s = *(const float4*)(sp + (size_t)g * AM_QT * AM_SS);
-                const float4 ta = *(const float4*)(tp + g * H), tb = *(const float4*)(tp + g * H + 4);
-                const float tv[8] = {ta.x, ta.y, ta.z, ta.w, tb.x, tb.y, tb.z, tb.w};
+                const ulonglong2 sv = *(const ulonglong2*)(sp + (size_t)g * AM_QT * AM_SS);
+                const ulonglong2* tg = (const ulonglong2*)(tp + (size_t)g * H * 2);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    acc[j][0] += tv[j] * s.x;
-                    acc[j][1] += tv[j] * s.y;
-                    acc[j][2] += tv[j] * s.z;
-                    acc[j][3] += tv[j] * s.w;
+                for (int jj = 0; jj < 4; ++jj) {
+                    const ulonglong2 tv = tg[jj];
+                    am_fma2(acc2[2 * jj][0], tv.x, sv.x);
+                    am_fma2(acc2[2 * jj][1], tv.x, sv.y);
+                    am_fma2(acc2[2 * jj + 1][0], tv.y, sv.x);
+                    am_fma2(acc2[2 * jj + 1][1], tv.y, sv.y);
                 }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc[j][0] = __uint_as_float((unsigned)acc2[j][0]);
+                acc[j][1] = __uint_as_float((unsigned)(acc2[j][0] >> 32));
+                acc[j][2] = __uint_as_float((unsigned)acc2[j][1]);
+                acc[j][3] = __uint_as_float((unsigned)(acc2[j][1] >> 32));
             }
             bool see[4];
 #pragma unroll
@@ -259,7 +277,7 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
                 float sum = 0.f;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    e[i] = (see[i] && m_new != -INFINITY) ? expf(acc[j][i] - m_new) : 0.f;
+                    e[i] = (see[i] && m_new != -INFINITY) ? exp2f(acc[j][i] - m_new) : 0.f;
                     e[i] = __bfloat162float(__float2bfloat16_rn(e[i]));
                     sum += e[i];
                 }
@@ -267,7 +285,7 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
                 sum += __shfl_xor_sync(gmask, sum, 2);
                 sum += __shfl_xor_sync(gmask, sum, 4);
                 const float alpha = (m_old == -INFINITY) ? (m_new == -INFINITY ? 1.f : 0.f)
-                                                         : expf(m_old - m_new);
+                                                         : exp2f(m_old - m_new);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[j][i] = e[i];
                 if (kg == 0) {
@@ -334,7 +352,7 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
         for (int i = tid; i < H * n_q; i += blockDim.x) {
             const int h = i / n_q, row = i - h * n_q;
             float* part = scratch + ((size_t)(q0 + t_first + row - first_token) * gridDim.z + blockIdx.z) * stride;
-            part[h] = m_s[h * AM_QT + row];
+            part[h] = m_s[h * AM_QT + row] * AM_LN2;           // the merge works with natural logarithms
             part[H + h] = l_s[h * AM_QT + row];
         }
 #pragma unroll
@@ -380,7 +398,7 @@ attention_mixed_mma_kernel(const bf16* __restrict__ rows, int row_stride, int ga
 
 extern "C" long long AM_NAME(rv_attention_mixed_mma_smem_d)(int H, int G) {
     return (long long)AM_KT * (G * RV_D + 8) * 2 + (long long)AM_KT * (G * RV_DV + 8) * 2 +
-           (long long)H * AM_QT * AM_SS * 4 + (long long)AM_QT * (H * RV_D + 8) * 2 + (long long)H * H * 4 +
+           (long long)H * AM_QT * AM_SS * 4 + (long long)AM_QT * (H * RV_D + 8) * 2 + (long long)H * H * 8 +
            3ll * H * AM_QT * 4;
 }
 

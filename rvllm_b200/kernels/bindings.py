@@ -801,7 +801,7 @@ class CudaOps:
             return False
         smem = 32 * (num_kv_heads * (head_dim + v_head_dim) + 16) * 2 \
             + num_heads * 16 * 40 * 4 + 16 * (num_heads * head_dim + 8) * 2 \
-            + num_heads * num_heads * 4 + num_heads * 192
+            + num_heads * num_heads * 8 + num_heads * 192
         return smem <= 227 * 1024
 
     def _mixed_lib(self, head_dim: int, v_head_dim: int):
