@@ -80,30 +80,57 @@ __global__ void __launch_bounds__(CH * NC) mingru_chunked_kernel(const float* __
     if (len <= RV_MINGRU_KEEP) {
         // short chunks: the gates of the first pass stay in registers for the second
         float ka[RV_MINGRU_KEEP], kb[RV_MINGRU_KEEP];
+        // every load of the chunk is requested before any gate is formed
 #pragma unroll
         for (int i = 0; i < RV_MINGRU_KEEP; ++i) {
-            ka[i] = 1.f;
+            ka[i] = 0.f;
             kb[i] = 0.f;
             if (live && b0 + i < b1) {
                 const float* row = rows + (size_t)(b0 + i) * 3 * width;
-                mingru_gate(row[c], row[width + c], bz, bx, ka[i], kb[i]);
+                ka[i] = row[c];
+                kb[i] = row[width + c];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < RV_MINGRU_KEEP; ++i) {
+            if (live && b0 + i < b1) {
+                mingru_gate(ka[i], kb[i], bz, bx, ka[i], kb[i]);
                 A *= ka[i];
                 B = ka[i] * B + kb[i];
+            } else {
+                ka[i] = 1.f;
+                kb[i] = 0.f;
             }
         }
         sa[k][threadIdx.x] = A;
         sb[k][threadIdx.x] = B;
+        // the gate rows of the second pass travel while the chunks' (A, B) are walked
+        float gv[RV_MINGRU_KEEP / 2];
+#pragma unroll
+        for (int i = 0; i < RV_MINGRU_KEEP / 2; ++i)
+            gv[i] = (live && b0 + i < b1) ? rows[(size_t)(b0 + i) * 3 * width + 2 * width + c] : 0.f;
         __syncthreads();
         float s = live ? state[(size_t)slot * width + c] : 0.f;
         for (int j = 0; j < k; ++j) s = sa[j][threadIdx.x] * s + sb[j][threadIdx.x];
         if (!live) return;
 #pragma unroll
-        for (int i = 0; i < RV_MINGRU_KEEP; ++i)
-            if (b0 + i < b1) {
-                s = ka[i] * s + kb[i];
-                const float g = rows[(size_t)(b0 + i) * 3 * width + 2 * width + c];
-                rv_store(out + (size_t)(b0 + i) * width + c, s * (g * rv_sigmoid(g)));
+        for (int half = 0; half < 2; ++half) {
+            if (half == 1) {
+#pragma unroll
+                for (int i = 0; i < RV_MINGRU_KEEP / 2; ++i) {
+                    const int t = b0 + RV_MINGRU_KEEP / 2 + i;
+                    gv[i] = t < b1 ? rows[(size_t)t * 3 * width + 2 * width + c] : 0.f;
+                }
             }
+#pragma unroll
+            for (int i = 0; i < RV_MINGRU_KEEP / 2; ++i) {
+                const int ii = half * (RV_MINGRU_KEEP / 2) + i;
+                if (b0 + ii < b1) {
+                    s = ka[ii] * s + kb[ii];
+                    rv_store(out + (size_t)(b0 + ii) * width + c, s * (gv[i] * rv_sigmoid(gv[i])));
+                }
+            }
+        }
         if (k == NC - 1) state[(size_t)slot * width + c] = s;
         return;
     }
