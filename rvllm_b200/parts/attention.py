@@ -16,6 +16,15 @@ j <= p, and with a window iff j > p - window.
 
 A call whose cache belongs to another call (`cache.owns` false) has no k and v of
 its own: it projects q only and reads the other call's pages.
+
+Options of the spec, each off at its default.  A value head of its own size.  A sink: the
+softmax's denominator holds one more term exp(sink) without a key or a value, a constant
+(`sink_score`; 0 gives p_j = exp(s_j) / (1 + sum exp(s_j))) or a learned number per head
+(`sinks`).  A unit norm of q and k (`qk_norm` of kind "rms_unit": x / sqrt(mean(x^2) + eps) per
+head, no weight).  A query temperature (`q_temp` = (coef, every)): the query at position p is
+multiplied by 1 + coef ln(floor((p + 1) / every) + 1), so scores grow slowly with the length
+of the context.  With the unit norm, the temperature or a value size of its own, norm,
+temperature and the cache write are `ops.qk_unit_write` after the one q|k|v product.
 """
 from __future__ import annotations
 
@@ -32,33 +41,48 @@ class Attention(Mixer):
     def _names(spec):
         n = spec.names
         return {k: n.get(k, k + ".weight") for k in
-                ("q_proj", "k_proj", "v_proj", "out_proj", "q_norm", "k_norm")}
+                ("q_proj", "k_proj", "v_proj", "out_proj", "q_norm", "k_norm", "sink")}
 
     @staticmethod
     def params(spec: AttentionSpec, owns_cache: bool = True):
         n = Attention._names(spec)
+        dv = spec.v_head_dim or spec.head_dim
         qd, kd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
         p = {n["q_proj"]: ParamDecl((qd, spec.hidden), "linear"),
-             n["out_proj"]: ParamDecl((spec.hidden, qd), "linear")}
+             n["out_proj"]: ParamDecl((spec.hidden, spec.num_heads * dv), "linear")}
         if owns_cache:
             p[n["k_proj"]] = ParamDecl((kd, spec.hidden), "linear")
-            p[n["v_proj"]] = ParamDecl((kd, spec.hidden), "linear")
-        if spec.qk_norm is not None:
+            p[n["v_proj"]] = ParamDecl((spec.num_kv_heads * dv, spec.hidden), "linear")
+        if Attention._weighted_norm(spec):
             p[n["q_norm"]] = ParamDecl((spec.head_dim,), "norm")
             if owns_cache:
                 p[n["k_norm"]] = ParamDecl((spec.head_dim,), "norm")
+        if spec.sinks:
+            p[n["sink"]] = ParamDecl((spec.num_heads,), "normal", mean=0.0, std=1.0)
         return p
 
     @staticmethod
+    def _weighted_norm(spec) -> bool:
+        return spec.qk_norm is not None and spec.qk_norm.kind != "rms_unit"
+
+    @staticmethod
+    def _plain(spec) -> bool:
+        """Whether the layer is the plain form that the fused q|k|v kernel serves."""
+        return (not spec.v_head_dim or spec.v_head_dim == spec.head_dim) and \
+            spec.q_temp is None and (spec.qk_norm is None or spec.qk_norm.kind != "rms_unit")
+
+    @staticmethod
     def cache_need(spec: AttentionSpec):
-        return PagedNeed(spec.num_kv_heads, spec.head_dim, spec.window)
+        dv = spec.v_head_dim or spec.head_dim
+        return PagedNeed(spec.num_kv_heads, spec.head_dim, spec.window,
+                         v_head_dim=dv if dv != spec.head_dim else None)
 
     @staticmethod
     def workspace_bytes(spec: AttentionSpec, ops, max_requests: int, max_context: int) -> int:
         sizer = getattr(ops, "attention_scratch_bytes", None)
         if sizer is None:
             return 0
-        return sizer(max_requests, spec.num_heads, spec.head_dim, max_context)
+        return sizer(max_requests, spec.num_heads, max(spec.head_dim, spec.v_head_dim), max_context)
 
     def __init__(self, spec: AttentionSpec, tensors, ops, dtype):
         if spec.num_heads % spec.num_kv_heads:
@@ -78,7 +102,16 @@ class Attention(Mixer):
         self.w_q = self.w_qkv[:spec.num_heads * spec.head_dim]
         self.w_out = tensors[n["out_proj"]].contiguous()
         self.q_norm = self.k_norm = None
-        if spec.qk_norm is not None:
+        self.v_dim = spec.v_head_dim or spec.head_dim
+        self.sinks = None
+        if spec.sinks and spec.sink_score is not None:
+            raise ValueError("attention: a sink is a constant or learned, not both")
+        if spec.sinks:
+            self.sinks = tensors[n["sink"]].to(torch.float32).contiguous()
+        elif spec.sink_score is not None:
+            self.sinks = torch.full((spec.num_heads,), float(spec.sink_score),
+                                    dtype=torch.float32, device=q.device)
+        if self._weighted_norm(spec):
             self.q_norm = tensors[n["q_norm"]].to(torch.float32).contiguous()
             if self.has_kv:
                 self.k_norm = tensors[n["k_norm"]].to(torch.float32).contiguous()
@@ -92,6 +125,8 @@ class Attention(Mixer):
             raise ValueError("attention: this call owns a cache but the block has no "
                              "key and value projections")
         group = ctx.groups[cache.group]
+        if not self._plain(s):
+            return self._forward_options(normed, ctx, cache, group)
         qkv = self.ops.linear_qk_norm_rope_write(
             normed, self.w_qkv if owns else self.w_q, s.num_heads,
             s.num_kv_heads if owns else 0, s.head_dim,
@@ -100,7 +135,27 @@ class Attention(Mixer):
             cache.k if owns else None, cache.v if owns else None, out_dtype=self.dtype)
         out = self.ops.new_rows(normed.shape[0], s.num_heads * s.head_dim, self.dtype, normed.device)
         self.ops.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim,
-                                 cache.k, cache.v, ctx, group, self.scale, s.window, out)
+                                 cache.k, cache.v, ctx, group, self.scale, s.window, out,
+                                 sinks=self.sinks)
+        return self.ops.linear(out, self.w_out, out_dtype=self.dtype)
+
+    def _forward_options(self, normed, ctx, cache, group):
+        s = self.spec
+        owns = cache.owns
+        if self.q_norm is not None or s.position.kind != "none":
+            raise ValueError("attention: a unit norm, a query temperature or a value size of "
+                             "its own goes with neither a weighted q/k norm nor a rotation")
+        kv = s.num_kv_heads if owns else 0
+        rows = self.ops.linear(normed, self.w_qkv if owns else self.w_q, out_dtype=self.dtype)
+        self.ops.qk_unit_write(rows, s.num_heads, kv, s.head_dim, self.v_dim,
+                               s.qk_norm.eps if s.qk_norm is not None else None, s.q_temp,
+                               ctx.positions, group.slot_mapping,
+                               cache.k if owns else None, cache.v if owns else None)
+        out = self.ops.new_rows(normed.shape[0], s.num_heads * self.v_dim, self.dtype,
+                                normed.device)
+        self.ops.paged_attention(rows, s.num_heads, s.num_kv_heads, s.head_dim,
+                                 cache.k, cache.v, ctx, group, self.scale, s.window, out,
+                                 sinks=self.sinks, v_head_dim=self.v_dim)
         return self.ops.linear(out, self.w_out, out_dtype=self.dtype)
 
 

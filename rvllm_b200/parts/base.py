@@ -29,15 +29,19 @@ class PagedNeed:
     are ever read again; `chunk`: only the positions of the newest chunk of `chunk` positions
     (counted from position 0) are.  Both tell the cache manager which pages it may take
     back early; neither changes the layout.  `v_head_dim`: size of a value head when it is
-    not the key size."""
+    not the key size.  `values` false: one row per token is all there is (a latent row that
+    keys and values are both made from); no value pages exist."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     chunk: Optional[int] = None
     v_head_dim: Optional[int] = None
+    values: bool = True
 
     @property
     def value_dim(self) -> int:
+        if not self.values:
+            return 0
         return self.v_head_dim if self.v_head_dim else self.head_dim
 
     def layout(self):

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from .base import FeedForward, register_feed_forward
-from .spec import DenseSpec, ParamDecl, SwiGLUSpec
+from .spec import DenseSpec, MoESpec, ParamDecl, SwiGLUSpec
 
 
 class SwiGLU(FeedForward):
@@ -83,3 +83,84 @@ class Dense(FeedForward):
 
 
 register_feed_forward("dense", Dense)
+
+
+class MoE(FeedForward):
+    """A mixture of SwiGLU experts (`MoESpec`).  For a token x:
+
+        s       = sigmoid(W_router x)                           float32
+        allowed = experts of the `keep` groups whose `group_top` best scores sum highest
+        chosen  = the `top` allowed experts with the largest s  (ties: the lower index)
+        y       = sum_{e chosen} s_e / (sum_chosen s + weight_eps) * down_e(silu(gate_e x) * up_e x)
+
+    The router matrix is kept in float32, so its product runs in float32 whatever the compute
+    type.  The experts' matrices are stacked ([experts, 2 ffn, hidden] gate over up, and
+    [experts, hidden, ffn]); `ops.moe_experts` chooses between a kernel that walks each token's
+    experts (few tokens) and grouped matrix products over the tokens sorted by expert.  A
+    token's result is a sum over its own experts in the order they were chosen, so it does not
+    depend on what else is in the batch.
+    """
+    SCORES = ("sigmoid",)
+
+    @staticmethod
+    def _names(spec):
+        n = spec.names
+        out = {"router": n.get("router", "router")}
+        for e in range(spec.experts):
+            for k in ("gate", "up", "down"):
+                out[(e, k)] = n.get("expert", "e{e}.{k}").format(e=e, k=k)
+        return out
+
+    @staticmethod
+    def _check(spec: MoESpec):
+        if spec.score not in MoE.SCORES:
+            raise ValueError(f"unknown router score {spec.score!r} (known: {MoE.SCORES})")
+        if spec.experts < 1 or not 1 <= spec.top <= spec.experts:
+            raise ValueError(f"a mixture of {spec.experts} experts cannot use {spec.top} a token")
+        if spec.groups < 1 or spec.experts % spec.groups or not 1 <= spec.keep <= spec.groups:
+            raise ValueError(f"{spec.experts} experts do not form {spec.groups} equal groups "
+                             f"of which {spec.keep} are kept")
+        if spec.keep * (spec.experts // spec.groups) < spec.top:
+            raise ValueError(f"{spec.keep} groups of {spec.experts // spec.groups} experts "
+                             f"cannot give {spec.top} experts")
+
+    @staticmethod
+    def params(spec: MoESpec):
+        MoE._check(spec)
+        n = MoE._names(spec)
+        p = {n["router"]: ParamDecl((spec.experts, spec.hidden), "normal", mean=0.0,
+                                    std=spec.hidden ** -0.5)}
+        for e in range(spec.experts):
+            p[n[(e, "gate")]] = ParamDecl((spec.ffn_dim, spec.hidden), "linear")
+            p[n[(e, "up")]] = ParamDecl((spec.ffn_dim, spec.hidden), "linear")
+            p[n[(e, "down")]] = ParamDecl((spec.hidden, spec.ffn_dim), "linear")
+        return p
+
+    def __init__(self, spec: MoESpec, tensors, ops, dtype):
+        self._check(spec)
+        self.spec = spec
+        self.ops = ops
+        self.dtype = dtype
+        n = self._names(spec)
+        self.router = tensors[n["router"]].to(torch.float32).contiguous()
+        first = tensors[n[(0, "gate")]]
+        self.gate_up = torch.stack([
+            torch.cat([tensors[n[(e, "gate")]].to(first.dtype),
+                       tensors[n[(e, "up")]].to(first.dtype)], dim=0)
+            for e in range(spec.experts)]).contiguous()                  # [E, 2F, W]
+        self.down = torch.stack([tensors[n[(e, "down")]].to(first.dtype)
+                                 for e in range(spec.experts)]).contiguous()   # [E, W, F]
+
+    def forward(self, normed, ctx):
+        s = self.spec
+        n = normed.shape[0]
+        logits = self.ops.linear(normed, self.router, out_dtype=torch.float32)
+        ids = torch.empty((n, s.top), dtype=torch.int32, device=normed.device)
+        weights = torch.empty((n, s.top), dtype=torch.float32, device=normed.device)
+        self.ops.moe_select(logits, s.groups, s.keep, s.group_top, s.weight_eps, ids, weights)
+        out = self.ops.new_rows(n, s.hidden, self.dtype, normed.device)
+        self.ops.moe_experts(normed, ids, weights, self.gate_up, self.down, out)
+        return out
+
+
+register_feed_forward("moe", MoE)

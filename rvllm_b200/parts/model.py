@@ -113,4 +113,7 @@ class Model:
                                device=self.device)
         normed = self.final_norm.add_norm(stream.resid, stream.pending, ctx,
                                           rows=ctx.logit_rows, delta_norm=stream.pending_norm)
-        return self.ops.linear(normed, self.head, out_dtype=torch.float32)
+        logits = self.ops.linear(normed, self.head, out_dtype=torch.float32)
+        if self.spec.logit_softcap:
+            self.ops.softcap(logits, self.spec.logit_softcap)
+        return logits

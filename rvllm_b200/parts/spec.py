@@ -73,6 +73,38 @@ class AttentionSpec(MixerSpec):
     scale: Optional[float] = None               # None: 1/sqrt(head_dim)
     # local tensor name -> suffix in the file
     names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    # Options that are off at their defaults.  `qk_norm` of kind "rms_unit" divides every query
+    # and key head by its root mean square and has no weight.
+    v_head_dim: int = 0                         # size of a value head (0: the key size)
+    sink_score: Optional[float] = None          # the softmax's denominator holds one more term
+                                                # exp(sink_score) that has no key and no value
+    sinks: bool = False                         # the same with a learned score per head
+                                                # (tensor "sink" [heads])
+    q_temp: Optional[Tuple[float, int]] = None  # (coef, every): the query at position p is
+                                                # multiplied by 1 + coef ln(floor((p+1)/every) + 1)
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Attention whose keys and values are both projections of one small latent row per token,
+    the only thing that is cached: c = rmsnorm(W_dkv x) [kv_rank]; per head k = W_uk c,
+    v = W_uv c.  No position encoding.
+
+    sinks       a learned score per head whose exponential joins the softmax's denominator
+                (tensor "sink" [heads])
+    out_gate    the concatenated heads are multiplied by sigmoid(W_g x) before the output
+                product (tensor "g" [heads * v_head_dim, hidden])
+    A call that reads another call's latent rows has no W_dkv.
+    """
+    num_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    kv_rank: int = 0
+    scale: Optional[float] = None               # None: 1/sqrt(head_dim)
+    norm_eps: float = 1e-6
+    sinks: bool = False
+    out_gate: bool = False
+    names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
 
 
 @dataclass(frozen=True)
@@ -132,6 +164,26 @@ class DenseSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class MoESpec(FeedForwardSpec):
+    """A mixture of `experts` SwiGLU feed-forwards of size `ffn_dim`, of which a token uses
+    `top`.  score: how router logits become scores ("sigmoid").  `groups` > 1: the experts
+    form that many equal groups of neighbours, a group's score is the sum of its
+    `group_top` largest scores, and only experts of the `keep` best groups can be chosen.
+    The chosen experts' scores, divided by their sum + `weight_eps`, weigh their outputs.
+    Tensors: "router" [experts, hidden]; per expert e "e<e>.gate", "e<e>.up" [ffn_dim, hidden],
+    "e<e>.down" [hidden, ffn_dim]."""
+    ffn_dim: int = 0
+    experts: int = 0
+    top: int = 0
+    groups: int = 1
+    keep: int = 1
+    group_top: int = 2
+    score: str = "sigmoid"
+    weight_eps: float = 1e-20
+    names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: which parts and how they are arranged.
 
@@ -175,5 +227,6 @@ class ModelSpec:
     final_norm_name: object                     # a name, or {local name: name in the file}
     head_name: Optional[str]                    # None: the head is the embedding table
     embedding_scale: Optional[float] = None
+    logit_softcap: Optional[float] = None       # c: logits <- c tanh(logits / c)
     bos_token_id: Optional[int] = None
     eos_token_id: Optional[int] = None

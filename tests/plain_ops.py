@@ -96,8 +96,9 @@ class PlainOps:
 
     # ---- attention over the pages ----------------------------------------------------
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
-                        ctx, group, scale, window, out):
+                        ctx, group, scale, window, out, sinks=None, v_head_dim=None):
         hd = head_dim
+        vd = v_head_dim or head_dim
         G = num_heads // num_kv_heads
         ps = group.page_size
         q_start = ctx.q_start.tolist()
@@ -115,13 +116,15 @@ class PlainOps:
                 keys = list(range(lo, p + 1))
                 idx = torch.tensor([table[j // ps] * ps + j % ps for j in keys])
                 k = _f(k_cache.view(-1, num_kv_heads, hd)[idx])      # [keys, kv, hd]
-                v = _f(v_cache.view(-1, num_kv_heads, hd)[idx])
+                v = _f(v_cache.view(-1, num_kv_heads, vd)[idx])
                 q = _f(qkv[t, :num_heads * hd]).reshape(num_heads, hd)
                 for h in range(num_heads):
                     g = h // G
                     s = (k[:, g] @ q[h]) * scale
-                    pr = torch.softmax(s, dim=0)
-                    out[t, h * hd:(h + 1) * hd] = (pr @ v[:, g]).to(out.dtype)
+                    if sinks is not None:
+                        s = torch.cat([s, _f(sinks[h:h + 1])])
+                    pr = torch.softmax(s, dim=0)[:idx.shape[0]]
+                    out[t, h * vd:(h + 1) * vd] = (pr @ v[:, g]).to(out.dtype)
 
     # ---- gated short convolution -----------------------------------------------------
     def short_conv(self, proj, filt, in_bias, conv_bias, state, ctx, out):
@@ -272,6 +275,84 @@ class PlainOps:
                 if gate_off >= 0:
                     o = o * torch.sigmoid(_f(rows[t, gate_off:gate_off + H * dv]))
                 out[t] = o.to(out.dtype)
+
+    # ---- unit norm of q and k, query temperature, cache write ---------------------------
+    def qk_unit_write(self, rows, num_heads, num_kv_heads, head_dim, v_head_dim, eps, q_temp,
+                      positions, slot_mapping, k_cache, v_cache):
+        n = rows.shape[0]
+        H, G, d, dv = num_heads, num_kv_heads, head_dim, v_head_dim
+
+        def unit(x):
+            return x if eps is None else x / (x.pow(2).mean(dim=-1, keepdim=True) + eps).sqrt()
+
+        q = unit(_f(rows[:, :H * d]).reshape(n, H, d))
+        if q_temp is not None:
+            coef, every = q_temp
+            steps = torch.div(positions.long() + 1, every, rounding_mode="floor") + 1
+            q = q * (1.0 + coef * torch.log(steps.to(torch.float32)))[:, None, None]
+        rows[:, :H * d] = q.reshape(n, H * d).to(rows.dtype)
+        if G:
+            k = unit(_f(rows[:, H * d:(H + G) * d]).reshape(n, G, d))
+            v = rows[:, (H + G) * d:(H + G) * d + G * dv].reshape(n, G, dv)
+            kc, vc = k_cache.view(-1, G, d), v_cache.view(-1, G, dv)
+            for t in range(n):
+                s = int(slot_mapping[t])
+                if s >= 0:
+                    kc[s] = k[t].to(kc.dtype)
+                    vc[s] = v[t].to(vc.dtype)
+
+    # ---- latent rows: norm and cache write ----------------------------------------------
+    def latent_norm_write(self, rows, offset, rank, weight, eps, slot_mapping, cache):
+        c = _f(rows[:, offset:offset + rank])
+        c = c / (c.pow(2).mean(dim=-1, keepdim=True) + eps).sqrt() * _f(weight)
+        pages = cache.view(-1, rank)
+        for t in range(rows.shape[0]):
+            s = int(slot_mapping[t])
+            if s >= 0:
+                pages[s] = c[t].to(pages.dtype)
+
+    # ---- one small product per head -------------------------------------------------------
+    def heads_product(self, rows, offset, heads, size, w, out):
+        x = _f(rows[:, offset:offset + heads * size]).reshape(-1, heads, size)
+        y = torch.einsum("nha,hab->nhb", x, _f(w))
+        out.copy_(y.reshape(out.shape).to(out.dtype))
+
+    def sigmoid_gate(self, x, rows, gate_off):
+        g = torch.sigmoid(_f(rows[:, gate_off:gate_off + x.shape[1]]))
+        x.copy_((_f(x) * g).to(x.dtype))
+
+    # ---- mixture of experts ---------------------------------------------------------------
+    def moe_select(self, logits, groups, keep, group_top, weight_eps, ids, weights):
+        n, E = logits.shape
+        top = ids.shape[1]
+        size = E // groups
+        for t in range(n):
+            s = torch.sigmoid(_f(logits[t]))
+            allowed = s.clone()
+            if groups > 1:
+                gs = s.reshape(groups, size).sort(dim=1, descending=True).values[:, :group_top].sum(1)
+                kept = torch.sort(gs, descending=True, stable=True).indices[:keep].tolist()
+                for g in range(groups):
+                    if g not in kept:
+                        allowed[g * size:(g + 1) * size] = -1.0
+            chosen = torch.sort(allowed, descending=True, stable=True).indices[:top]
+            ids[t] = chosen.to(torch.int32)
+            weights[t] = s[chosen] / (s[chosen].sum() + weight_eps)
+
+    def moe_experts(self, x, ids, weights, gate_up, down, out):
+        n, top = ids.shape
+        F = down.shape[2]
+        y = torch.zeros((n, out.shape[1]), dtype=torch.float32)
+        for t in range(n):
+            for k in range(top):
+                e = int(ids[t, k])
+                gu = _f(gate_up[e]) @ _f(x[t])
+                act = (torch.nn.functional.silu(gu[:F]) * gu[F:]).to(x.dtype)
+                y[t] += float(weights[t, k]) * (_f(down[e]) @ _f(act))
+        out.copy_(y.to(out.dtype))
+
+    def softcap(self, logits, cap):
+        logits.copy_(cap * torch.tanh(logits / cap))
 
     # ---- sampling --------------------------------------------------------------------
     def argmax(self, logits):
