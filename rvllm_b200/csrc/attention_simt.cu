@@ -16,6 +16,12 @@
 //
 // A key at position j is visible to the query at position p iff j <= p, and with a
 // window iff j > p - window; the softmax is the online form (running maximum and sum).
+// Two options.  `vd`: the size of a value head when it is not the key size `hd` (the value
+// pages are then [slots, kv heads, vd]).  `sinks` (float32, one per query head, or null):
+// the softmax's denominator holds one more term exp(sinks[h]) that has no key and no value;
+// it enters as the initial running maximum with a sum of 1, in the split form once, in the
+// merge.  Key sizes that are no multiple of 8 (bfloat16) or 4 (float32) elements take scalar
+// loads.
 // Reference counterparts: kv_gather.cu (twice), a batched SGEMM, mask_add_broadcast.cu,
 // softmax.cu, a batched SGEMM and transposes (src/cuda/model.rs:528-581).
 // Plain reference: tests/plain_ops.py paged_attention.
@@ -55,6 +61,16 @@ __device__ __forceinline__ float rv_dot_row(const float* __restrict__ q,
     return s;
 }
 
+// any head size: vector loads when the rows allow them, else one element at a time
+template <typename T>
+__device__ __forceinline__ float rv_dot_any(const float* __restrict__ q, const T* __restrict__ k,
+                                            int hd, bool vec) {
+    if (vec) return rv_dot_row(q, k, hd);
+    float s = 0.f;
+    for (int d = 0; d < hd; ++d) s += q[d] * rv_load(k + d);
+    return s;
+}
+
 // ---------------------------------------------------------------------------------
 template <typename T, int DPL>
 __global__ void paged_attention_warp_kernel(
@@ -62,9 +78,11 @@ __global__ void paged_attention_warp_kernel(
     const T* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
     const int* __restrict__ token_req, T* __restrict__ out, int first_token, int n_tokens,
-    int num_heads, int num_kv_heads, int hd, int page_size, float scale, int window) {
+    int num_heads, int num_kv_heads, int hd, int page_size, float scale, int window, int vd,
+    const float* __restrict__ sinks) {
     rv_pdl_prologue();
     constexpr bool kFast = sizeof(T) == 2;
+    const bool vec = hd % (16 / (int)sizeof(T)) == 0;
     extern __shared__ float q_smem[];   // [warps per block][hd]
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + wib;
@@ -74,9 +92,9 @@ __global__ void paged_attention_warp_kernel(
     const int g = h / (num_heads / num_kv_heads);
     const int r = token_req[t];
     const int clen = ctx_lens[r];
-    T* o = out + (size_t)t * num_heads * hd + (size_t)h * hd;
+    T* o = out + (size_t)t * num_heads * vd + (size_t)h * vd;
     if (clen == 0) {
-        for (int d = lane; d < hd; d += 32) rv_store(o + d, 0.f);
+        for (int d = lane; d < vd; d += 32) rv_store(o + d, 0.f);
         return;
     }
     const int qs = q_start[r];
@@ -87,11 +105,11 @@ __global__ void paged_attention_warp_kernel(
     for (int d = lane; d < hd; d += 32) qv[d] = rv_load(qrow + d);
     __syncwarp();
 
-    float m = -INFINITY, l = 0.f, acc[DPL];
+    float m = sinks ? sinks[h] : -INFINITY, l = sinks ? 1.f : 0.f, acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
     const int* table = block_table + (size_t)r * max_blocks;
-    const size_t row = (size_t)num_kv_heads * hd;
+    const size_t row = (size_t)num_kv_heads * hd, vrow_len = (size_t)num_kv_heads * vd;
 
     for (int base = lo & ~31; base <= p; base += 32) {
         const int j = base + lane;
@@ -100,7 +118,7 @@ __global__ void paged_attention_warp_kernel(
         float s = -INFINITY;
         if (valid) {
             slot = table[j / page_size] * page_size + j % page_size;
-            s = rv_dot_row(qv, k_cache + (size_t)slot * row + (size_t)g * hd, hd) * scale;
+            s = rv_dot_any(qv, k_cache + (size_t)slot * row + (size_t)g * hd, hd, vec) * scale;
         }
         const float m_new = fmaxf(m, rv_warp_max(s));
         const float pj = valid ? rv_exp<kFast>(s - m_new) : 0.f;
@@ -114,11 +132,11 @@ __global__ void paged_attention_warp_kernel(
             const float pk = __shfl_sync(0xffffffffu, pj, jj);
             const int sk = __shfl_sync(0xffffffffu, slot, jj);
             if (pk != 0.f) {
-                const T* vrow = v_cache + (size_t)sk * row + (size_t)g * hd;
+                const T* vrow = v_cache + (size_t)sk * vrow_len + (size_t)g * vd;
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) {
                     const int d = lane + 32 * i;
-                    if (d < hd) acc[i] += pk * rv_load(vrow + d);
+                    if (d < vd) acc[i] += pk * rv_load(vrow + d);
                 }
             }
         }
@@ -126,7 +144,7 @@ __global__ void paged_attention_warp_kernel(
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) rv_store(o + d, acc[i] / l);
+        if (d < vd) rv_store(o + d, acc[i] / l);
     }
 }
 
@@ -139,10 +157,11 @@ __global__ void __launch_bounds__(128) paged_attention_decode_kernel(
     const T* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ ctx_lens, float* __restrict__ part_o, float2* __restrict__ part_ml,
     int max_splits, int num_heads, int num_kv_heads, int hd, int page_size, float scale,
-    int window) {
+    int window, int vd) {
     rv_pdl_prologue();
     constexpr bool kFast = sizeof(T) == 2;
     constexpr int GT = RV_ATTN_GT;
+    const bool vec = hd % (16 / (int)sizeof(T)) == 0;
     extern __shared__ float smem[];
     const int G = num_heads / num_kv_heads;
     const int tiles = (G + GT - 1) / GT;
@@ -163,7 +182,7 @@ __global__ void __launch_bounds__(128) paged_attention_decode_kernel(
     float* qv = smem;                                // [GT][hd]
     float* ps = qv + GT * hd;                        // [4 warps][32][GT]
     int* ss = (int*)(ps + 4 * 32 * GT);              // [4 warps][32]
-    float* red = (float*)(ss + 4 * 32);              // [4 warps][GT][hd + 2]
+    float* red = (float*)(ss + 4 * 32);              // [4 warps][GT][vd + 2]
     for (int i = threadIdx.x; i < GT * hd; i += blockDim.x) {
         const int gi = i / hd, d = i - gi * hd;
         qv[i] = gi < gcount ? rv_load(q + (size_t)r * q_stride + (size_t)(h0 + gi) * hd + d) : 0.f;
@@ -179,7 +198,7 @@ __global__ void __launch_bounds__(128) paged_attention_decode_kernel(
         for (int i = 0; i < DPL; ++i) acc[gi][i] = 0.f;
     }
     const int* table = block_table + (size_t)r * max_blocks;
-    const size_t row = (size_t)num_kv_heads * hd;
+    const size_t row = (size_t)num_kv_heads * hd, vrow_len = (size_t)num_kv_heads * vd;
     float* my_p = ps + w * 32 * GT;
     int* my_s = ss + w * 32;
 
@@ -197,7 +216,7 @@ __global__ void __launch_bounds__(128) paged_attention_decode_kernel(
             const T* krow = k_cache + (size_t)slot * row + (size_t)g * hd;
 #pragma unroll
             for (int gi = 0; gi < GT; ++gi)
-                if (gi < gcount) s[gi] = rv_dot_row(qv + gi * hd, krow, hd) * scale;
+                if (gi < gcount) s[gi] = rv_dot_any(qv + gi * hd, krow, hd, vec) * scale;
         }
         my_s[lane] = slot;
 #pragma unroll
@@ -218,14 +237,14 @@ __global__ void __launch_bounds__(128) paged_attention_decode_kernel(
         __syncwarp();
         const int count = min(32, k1 - base + 1);
         for (int jj = max(0, k0 - base); jj < count; ++jj) {
-            const T* vrow = v_cache + (size_t)my_s[jj] * row + (size_t)g * hd;
+            const T* vrow = v_cache + (size_t)my_s[jj] * vrow_len + (size_t)g * vd;
             float pk[GT];
 #pragma unroll
             for (int gi = 0; gi < GT; ++gi) pk[gi] = my_p[jj * GT + gi];
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) {
+                if (d < vd) {
                     const float v = rv_load(vrow + d);
 #pragma unroll
                     for (int gi = 0; gi < GT; ++gi) acc[gi][i] += pk[gi] * v;
@@ -235,34 +254,34 @@ __global__ void __launch_bounds__(128) paged_attention_decode_kernel(
         __syncwarp();
     }
     // combine the four warps in warp order
-    const int rs = hd + 2;
+    const int rs = vd + 2;
 #pragma unroll
     for (int gi = 0; gi < GT; ++gi) {
         float* mine = red + (size_t)(w * GT + gi) * rs;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
             const int d = lane + 32 * i;
-            if (d < hd) mine[d] = acc[gi][i];
+            if (d < vd) mine[d] = acc[gi][i];
         }
         if (lane == 0) {
-            mine[hd] = m[gi];
-            mine[hd + 1] = l[gi];
+            mine[vd] = m[gi];
+            mine[vd + 1] = l[gi];
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < gcount * hd; i += blockDim.x) {
-        const int gi = i / hd, d = i - gi * hd;
+    for (int i = threadIdx.x; i < gcount * vd; i += blockDim.x) {
+        const int gi = i / vd, d = i - gi * vd;
         float M = -INFINITY;
-        for (int ww = 0; ww < 4; ++ww) M = fmaxf(M, red[(size_t)(ww * GT + gi) * rs + hd]);
+        for (int ww = 0; ww < 4; ++ww) M = fmaxf(M, red[(size_t)(ww * GT + gi) * rs + vd]);
         float L = 0.f, O = 0.f;
         for (int ww = 0; ww < 4; ++ww) {
             const float* src = red + (size_t)(ww * GT + gi) * rs;
-            const float f = src[hd] == -INFINITY ? 0.f : rv_exp<kFast>(src[hd] - M);
-            L += src[hd + 1] * f;
+            const float f = src[vd] == -INFINITY ? 0.f : rv_exp<kFast>(src[vd] - M);
+            L += src[vd + 1] * f;
             O += src[d] * f;
         }
         const size_t slot = ((size_t)r * num_heads + h0 + gi) * max_splits + split;
-        part_o[slot * hd + d] = O;
+        part_o[slot * vd + d] = O;
         if (d == 0) part_ml[slot] = make_float2(M, L);
     }
 }
@@ -272,11 +291,12 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ part_o,
                                              const float2* __restrict__ part_ml,
                                              const int* __restrict__ ctx_lens, T* __restrict__ out,
                                              int max_splits, int num_heads, int hd, int window,
-                                             int split_keys) {
+                                             int split_keys, const float* __restrict__ sinks) {
     rv_pdl_launch_dependents();
     constexpr bool kFast = sizeof(T) == 2;
     const int r = blockIdx.y, h = blockIdx.x;
     const int clen = ctx_lens[r];                 // the step's index array: before the wait
+    const float sink = sinks ? sinks[h] : -INFINITY;      // a constant of the layer
     rv_pdl_wait();
     T* o = out + ((size_t)r * num_heads + h) * hd;
     if (clen == 0) {
@@ -297,7 +317,7 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ part_o,
     // a group costs one memory latency, not sixteen.
     constexpr int GROUP = 16;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float M = -INFINITY, L = 0.f, O = 0.f;
+        float M = sink, L = sinks ? 1.f : 0.f, O = 0.f;     // the sink counts once, here
         for (int sb = s0; sb <= s1; sb += GROUP) {
             float2 ml[GROUP];
             float po[GROUP];
@@ -327,15 +347,15 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ part_o,
 }
 
 // ---------------------------------------------------------------------------------
-static int check_attention_sizes(const char* name, int num_heads, int num_kv_heads, int hd,
+static int check_attention_sizes(const char* name, int num_heads, int num_kv_heads, int hd, int vd,
                                  int page_size, int dtype) {
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads)
         RV_FAIL("%s: invalid head counts: %d query, %d KV", name, num_heads, num_kv_heads);
-    const int step = dtype == RV_DTYPE_BF16 ? 8 : 4;
-    if (hd <= 0 || hd % step || hd > 32 * RV_ATTN_MAX_DPL)
-        RV_FAIL("%s: head size %d is not supported (a multiple of %d, at most %d)", name, hd, step,
+    if (hd <= 0 || hd > 32 * RV_ATTN_MAX_DPL || vd <= 0 || vd > 32 * RV_ATTN_MAX_DPL)
+        RV_FAIL("%s: head sizes %d and %d are not supported (at most %d)", name, hd, vd,
                 32 * RV_ATTN_MAX_DPL);
     if (page_size <= 0) RV_FAIL("%s: bad page size %d", name, page_size);
+    (void)dtype;
     return 0;
 }
 
@@ -349,14 +369,17 @@ static int check_attention_sizes(const char* name, int num_heads, int num_kv_hea
         default: { constexpr int DPL = 8; __VA_ARGS__; break; }           \
     }
 
-extern "C" int rv_paged_attention_warp(const void* q, int dtype, int q_stride, const void* k_cache,
-                                       const void* v_cache, const int* block_table, int max_blocks,
-                                       const int* q_start, const int* ctx_lens,
-                                       const int* token_req, void* out, int first_token,
-                                       int n_tokens, int num_heads, int num_kv_heads, int hd,
-                                       int page_size, float scale, int window, void* stream) {
+// `vd`: size of a value head; `sinks`: float32 [num_heads] or null (see the top of the file).
+extern "C" int rv_paged_attention_warp_ex(const void* q, int dtype, int q_stride,
+                                          const void* k_cache, const void* v_cache,
+                                          const int* block_table, int max_blocks,
+                                          const int* q_start, const int* ctx_lens,
+                                          const int* token_req, void* out, int first_token,
+                                          int n_tokens, int num_heads, int num_kv_heads, int hd,
+                                          int page_size, float scale, int window, int vd,
+                                          const float* sinks, void* stream) {
     if (n_tokens == 0) return 0;
-    if (check_attention_sizes("paged_attention", num_heads, num_kv_heads, hd, page_size, dtype))
+    if (check_attention_sizes("paged_attention", num_heads, num_kv_heads, hd, vd, page_size, dtype))
         return 1;
     const int wpb = 4;
     const long long warps = (long long)n_tokens * num_heads;
@@ -365,20 +388,75 @@ extern "C" int rv_paged_attention_warp(const void* q, int dtype, int q_stride, c
     const size_t smem = (size_t)wpb * hd * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     RV_DISPATCH_DTYPE(dtype, "paged_attention",
-        RV_DISPATCH_DPL(hd, (rv_launch(paged_attention_warp_kernel<T, DPL>, dim3((int)blocks), dim3(wpb * 32), smem, s, 
+        RV_DISPATCH_DPL(vd, (rv_launch(paged_attention_warp_kernel<T, DPL>, dim3((int)blocks), dim3(wpb * 32), smem, s, 
             (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, max_blocks,
             q_start, ctx_lens, token_req, (T*)out, first_token, n_tokens, num_heads, num_kv_heads,
-            hd, page_size, scale, window))));
+            hd, page_size, scale, window, vd, sinks))));
     RV_CHECK_LAUNCH("paged_attention");
     return 0;
 }
 
-// Bytes of scratch rv_paged_attention_decode needs: part_o then part_ml.
+extern "C" int rv_paged_attention_warp(const void* q, int dtype, int q_stride, const void* k_cache,
+                                       const void* v_cache, const int* block_table, int max_blocks,
+                                       const int* q_start, const int* ctx_lens,
+                                       const int* token_req, void* out, int first_token,
+                                       int n_tokens, int num_heads, int num_kv_heads, int hd,
+                                       int page_size, float scale, int window, void* stream) {
+    return rv_paged_attention_warp_ex(q, dtype, q_stride, k_cache, v_cache, block_table, max_blocks,
+                                      q_start, ctx_lens, token_req, out, first_token, n_tokens,
+                                      num_heads, num_kv_heads, hd, page_size, scale, window, hd,
+                                      nullptr, stream);
+}
+
+// Bytes of scratch rv_paged_attention_decode needs: part_o then part_ml (`hd`: the value size).
 extern "C" long long rv_paged_attention_decode_scratch_bytes(int n_reqs, int num_heads, int hd,
                                                              int max_ctx_len) {
     const long long splits = (max_ctx_len + RV_ATTN_SPLIT - 1) / RV_ATTN_SPLIT;
     const long long slots = (long long)n_reqs * num_heads * (splits > 0 ? splits : 1);
     return slots * hd * 4 + slots * 8;
+}
+
+static int merge_threads(int hd) { return hd < 32 ? 32 : (hd > 128 ? 128 : ((hd + 31) / 32) * 32); }
+
+extern "C" int rv_paged_attention_decode_ex(const void* q, int dtype, int q_stride,
+                                            const void* k_cache, const void* v_cache,
+                                            const int* block_table, int max_blocks,
+                                            const int* ctx_lens, void* out, void* scratch,
+                                            long long scratch_bytes, int n_reqs, int max_ctx_len,
+                                            int num_heads, int num_kv_heads, int hd, int page_size,
+                                            float scale, int window, int vd, const float* sinks,
+                                            void* stream) {
+    if (n_reqs == 0) return 0;
+    if (check_attention_sizes("paged_attention_decode", num_heads, num_kv_heads, hd, vd, page_size,
+                              dtype))
+        return 1;
+    int max_splits = (max_ctx_len + RV_ATTN_SPLIT - 1) / RV_ATTN_SPLIT;
+    if (max_splits < 1) max_splits = 1;
+    if (rv_paged_attention_decode_scratch_bytes(n_reqs, num_heads, vd, max_ctx_len) > scratch_bytes)
+        RV_FAIL("paged_attention_decode: scratch of %lld bytes is too small", scratch_bytes);
+    if (n_reqs > 65535 || max_splits > 65535) RV_FAIL("paged_attention_decode: batch too large");
+    const size_t slots = (size_t)n_reqs * num_heads * max_splits;
+    float* part_o = (float*)scratch;
+    float2* part_ml = (float2*)((char*)scratch + slots * vd * 4);
+    const int G = num_heads / num_kv_heads;
+    const int tiles = (G + RV_ATTN_GT - 1) / RV_ATTN_GT;
+    dim3 grid(num_kv_heads * tiles, n_reqs, max_splits);
+    const size_t smem = (size_t)(RV_ATTN_GT * hd + 4 * 32 * RV_ATTN_GT + 4 * 32 +
+                                 4 * RV_ATTN_GT * (vd + 2)) * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    RV_DISPATCH_DTYPE(dtype, "paged_attention_decode",
+        RV_DISPATCH_DPL(vd, (rv_launch(paged_attention_decode_kernel<T, DPL>, dim3(grid), dim3(128), smem, s, 
+            (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, max_blocks,
+            ctx_lens, part_o, part_ml, max_splits, num_heads, num_kv_heads, hd, page_size, scale,
+            window, vd))));
+    RV_CHECK_LAUNCH("paged_attention_decode");
+    dim3 mgrid(num_heads, n_reqs);
+    RV_DISPATCH_DTYPE(dtype, "paged_attention_merge",
+        (rv_launch(paged_attention_merge_kernel<T>, dim3(mgrid), dim3(merge_threads(vd)), 0, s, 
+            part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, vd, window, RV_ATTN_SPLIT,
+            sinks)));
+    RV_CHECK_LAUNCH("paged_attention_merge");
+    return 0;
 }
 
 extern "C" int rv_paged_attention_decode(const void* q, int dtype, int q_stride,
@@ -388,43 +466,18 @@ extern "C" int rv_paged_attention_decode(const void* q, int dtype, int q_stride,
                                          long long scratch_bytes, int n_reqs, int max_ctx_len,
                                          int num_heads, int num_kv_heads, int hd, int page_size,
                                          float scale, int window, void* stream) {
-    if (n_reqs == 0) return 0;
-    if (check_attention_sizes("paged_attention_decode", num_heads, num_kv_heads, hd, page_size,
-                              dtype))
-        return 1;
-    int max_splits = (max_ctx_len + RV_ATTN_SPLIT - 1) / RV_ATTN_SPLIT;
-    if (max_splits < 1) max_splits = 1;
-    if (rv_paged_attention_decode_scratch_bytes(n_reqs, num_heads, hd, max_ctx_len) > scratch_bytes)
-        RV_FAIL("paged_attention_decode: scratch of %lld bytes is too small", scratch_bytes);
-    if (n_reqs > 65535 || max_splits > 65535) RV_FAIL("paged_attention_decode: batch too large");
-    const size_t slots = (size_t)n_reqs * num_heads * max_splits;
-    float* part_o = (float*)scratch;
-    float2* part_ml = (float2*)((char*)scratch + slots * hd * 4);
-    const int G = num_heads / num_kv_heads;
-    const int tiles = (G + RV_ATTN_GT - 1) / RV_ATTN_GT;
-    dim3 grid(num_kv_heads * tiles, n_reqs, max_splits);
-    const size_t smem = (size_t)(RV_ATTN_GT * hd + 4 * 32 * RV_ATTN_GT + 4 * 32 +
-                                 4 * RV_ATTN_GT * (hd + 2)) * sizeof(float);
-    cudaStream_t s = (cudaStream_t)stream;
-    RV_DISPATCH_DTYPE(dtype, "paged_attention_decode",
-        RV_DISPATCH_DPL(hd, (rv_launch(paged_attention_decode_kernel<T, DPL>, dim3(grid), dim3(128), smem, s, 
-            (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, max_blocks,
-            ctx_lens, part_o, part_ml, max_splits, num_heads, num_kv_heads, hd, page_size, scale,
-            window))));
-    RV_CHECK_LAUNCH("paged_attention_decode");
-    dim3 mgrid(num_heads, n_reqs);
-    RV_DISPATCH_DTYPE(dtype, "paged_attention_merge",
-        (rv_launch(paged_attention_merge_kernel<T>, dim3(mgrid), dim3(hd < 32 ? 32 : (hd > 128 ? 128 : ((hd + 31) / 32) * 32)), 0, s, 
-            part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window, RV_ATTN_SPLIT)));
-    RV_CHECK_LAUNCH("paged_attention_merge");
-    return 0;
+    return rv_paged_attention_decode_ex(q, dtype, q_stride, k_cache, v_cache, block_table,
+                                        max_blocks, ctx_lens, out, scratch, scratch_bytes, n_reqs,
+                                        max_ctx_len, num_heads, num_kv_heads, hd, page_size, scale,
+                                        window, hd, nullptr, stream);
 }
 
 // The merge step alone, for partial results written by another kernel (attention_mma.cu)
-// in the same scratch layout.
-extern "C" int rv_paged_attention_merge(const void* scratch, const int* ctx_lens, void* out,
-                                        int dtype, int n_reqs, int max_ctx_len, int num_heads,
-                                        int hd, int window, int split_keys, void* stream) {
+// in the same scratch layout.  `hd`: the value size; `sinks`: float32 [num_heads] or null.
+extern "C" int rv_paged_attention_merge_ex(const void* scratch, const int* ctx_lens, void* out,
+                                           int dtype, int n_reqs, int max_ctx_len, int num_heads,
+                                           int hd, int window, int split_keys, const float* sinks,
+                                           void* stream) {
     if (n_reqs == 0) return 0;
     if (split_keys <= 0) RV_FAIL("paged_attention_merge: bad split size");
     int max_splits = (max_ctx_len + split_keys - 1) / split_keys;
@@ -435,10 +488,17 @@ extern "C" int rv_paged_attention_merge(const void* scratch, const int* ctx_lens
     const float* part_o = (const float*)scratch;
     const float2* part_ml = (const float2*)((const char*)scratch + slots * hd * 4);
     dim3 mgrid(num_heads, n_reqs);
-    const int threads = hd < 32 ? 32 : (hd > 128 ? 128 : ((hd + 31) / 32) * 32);
     RV_DISPATCH_DTYPE(dtype, "paged_attention_merge",
-        (rv_launch(paged_attention_merge_kernel<T>, dim3(mgrid), dim3(threads), 0, (cudaStream_t)stream, 
-            part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window, split_keys)));
+        (rv_launch(paged_attention_merge_kernel<T>, dim3(mgrid), dim3(merge_threads(hd)), 0, (cudaStream_t)stream, 
+            part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window, split_keys,
+            sinks)));
     RV_CHECK_LAUNCH("paged_attention_merge");
     return 0;
+}
+
+extern "C" int rv_paged_attention_merge(const void* scratch, const int* ctx_lens, void* out,
+                                        int dtype, int n_reqs, int max_ctx_len, int num_heads,
+                                        int hd, int window, int split_keys, void* stream) {
+    return rv_paged_attention_merge_ex(scratch, ctx_lens, out, dtype, n_reqs, max_ctx_len,
+                                       num_heads, hd, window, split_keys, nullptr, stream);
 }

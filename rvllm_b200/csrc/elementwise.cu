@@ -293,3 +293,22 @@ extern "C" int rv_add_bias(void* x, int dtype, const float* bias, int n_rows, in
     RV_CHECK_LAUNCH("add_bias");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------
+// x <- cap * tanh(x / cap), in place on float32 logits.
+__global__ void softcap_kernel(float* __restrict__ x, float cap, size_t total) {
+    rv_pdl_prologue();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int rv_softcap(float* x, long long total, float cap, void* stream) {
+    if (total == 0) return 0;
+    if (total < 0 || !(cap > 0.f)) RV_FAIL("softcap: bad sizes or a cap that is not positive");
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    rv_launch(softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, cap,
+              (size_t)total);
+    RV_CHECK_LAUNCH("softcap");
+    return 0;
+}

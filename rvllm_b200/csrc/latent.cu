@@ -1,0 +1,80 @@
+// Small kernels around an attention over latent rows.
+//
+//   latent_norm_write   rows [N, row_stride] carry a latent row of `rank` values at column
+//                       `offset`; it is RMS-normed (x / sqrt(mean(x^2) + eps) * weight, float32)
+//                       and written to the page slot of its token, which is all that the cache
+//                       keeps of the token.  One warp per token.
+//   sigmoid_gate        x[n, i] <- x[n, i] * sigmoid(rows[n, gate_off + i]): the gate on the
+//                       concatenated heads before the output product.  Sigmoid and product are
+//                       float32, rounded once.
+// Plain references: tests/plain_ops.py latent_norm_write, sigmoid_gate.
+#include "common.cuh"
+
+template <typename T>
+__global__ void latent_norm_write_kernel(const T* __restrict__ rows, int row_stride, int n_tokens,
+                                         int offset, int rank, const float* __restrict__ weight,
+                                         float eps, const int* __restrict__ slot_mapping,
+                                         T* __restrict__ cache) {
+    rv_pdl_launch_dependents();
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= n_tokens) return;
+    const int t = (int)warp;
+    const int slot = slot_mapping[t];
+    rv_pdl_wait();
+    if (slot < 0) return;
+    const T* src = rows + (size_t)t * row_stride + offset;
+    float ss = 0.f;
+    for (int i = lane; i < rank; i += 32) {
+        const float x = rv_load(src + i);
+        ss += x * x;
+    }
+    ss = rv_warp_sum(ss);
+    const float rms = sqrtf(ss / (float)rank + eps);
+    T* dst = cache + (size_t)slot * rank;
+    for (int i = lane; i < rank; i += 32) rv_store(dst + i, rv_load(src + i) / rms * weight[i]);
+}
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, int width, const T* __restrict__ rows,
+                                    int row_stride, int gate_off, long long total) {
+    rv_pdl_prologue();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long n = i / width;
+    const int c = (int)(i - n * width);
+    const float g = rv_load(rows + n * row_stride + gate_off + c);
+    rv_store(x + i, rv_load(x + i) / (1.f + expf(-g)));
+}
+
+extern "C" int rv_latent_norm_write(const void* rows, int dtype, int row_stride, int n_tokens,
+                                    int offset, int rank, const float* weight, float eps,
+                                    const int* slot_mapping, void* cache, void* stream) {
+    if (n_tokens == 0) return 0;
+    if (n_tokens < 0 || rank <= 0 || offset < 0 || row_stride < offset + rank)
+        RV_FAIL("latent_norm_write: bad sizes");
+    if (!weight || !slot_mapping || !cache) RV_FAIL("latent_norm_write: a pointer is missing");
+    const long long blocks = ((long long)n_tokens + 3) / 4;
+    RV_DISPATCH_DTYPE(dtype, "latent_norm_write",
+                      (rv_launch(latent_norm_write_kernel<T>, dim3((int)blocks), dim3(128), 0,
+                                 (cudaStream_t)stream, (const T*)rows, row_stride, n_tokens, offset,
+                                 rank, weight, eps, slot_mapping, (T*)cache)));
+    RV_CHECK_LAUNCH("latent_norm_write");
+    return 0;
+}
+
+extern "C" int rv_sigmoid_gate(void* x, int dtype, int n, int width, const void* rows,
+                               int row_stride, int gate_off, void* stream) {
+    if (n == 0) return 0;
+    if (n < 0 || width <= 0 || gate_off < 0 || row_stride < gate_off + width)
+        RV_FAIL("sigmoid_gate: bad sizes");
+    const long long total = (long long)n * width;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) RV_FAIL("sigmoid_gate: too many values");
+    RV_DISPATCH_DTYPE(dtype, "sigmoid_gate",
+                      (rv_launch(sigmoid_gate_kernel<T>, dim3((int)blocks), dim3(256), 0,
+                                 (cudaStream_t)stream, (T*)x, width, (const T*)rows, row_stride,
+                                 gate_off, total)));
+    RV_CHECK_LAUNCH("sigmoid_gate");
+    return 0;
+}

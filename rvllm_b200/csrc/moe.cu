@@ -1,0 +1,243 @@
+// Mixture of experts: the choice of a token's experts, and the experts' SwiGLU feed-forwards
+// walked token by token (the form for few tokens and for float32; moe_grouped.cu has the
+// grouped matrix products for many bfloat16 tokens).
+//
+//   moe_select     logits float32 [N, E] -> ids int32 [N, top], weights float32 [N, top].
+//                  s = sigmoid(logits); with `groups` > 1 the experts form that many equal
+//                  groups of neighbours, a group's score is the sum of its `group_top` largest
+//                  s, and only experts of the `keep` best groups can be chosen; the `top`
+//                  largest allowed s are chosen (ties: the lower index first, for groups too);
+//                  weights = chosen s / (their sum + weight_eps).  One warp per token.
+//   moe_gate_up    act[pair, f] = silu(<gate_e[f], x_t>) * <up_e[f], x_t> for pair = t * top + k,
+//                  e = ids[t, k]; gate_up is [E, 2F, W] (gate rows, then up rows).
+//   moe_down       out[t, w] = sum_k weights[t, k] * <down_e(k)[w], act[t * top + k]>, the sum in
+//                  the order of k; down is [E, W, F].
+// Dot products and the activation are float32; act is rounded to the storage type.
+// Plain references: tests/plain_ops.py moe_select, moe_experts.
+#include "common.cuh"
+
+#define MOE_MAX_GROUP_TOP 8
+
+// (value, index) of the largest sc[e] over e in [lo, hi), ties to the lower index; whole warp.
+__device__ __forceinline__ void moe_warp_argmax(const float* sc, int lo, int hi, int lane,
+                                                float& best, int& idx) {
+    best = -INFINITY;
+    idx = 0x7fffffff;
+    for (int e = lo + lane; e < hi; e += 32) {
+        const float v = sc[e];
+        if (v > best) {
+            best = v;
+            idx = e;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) {
+            best = ov;
+            idx = oi;
+        }
+    }
+    if (idx == 0x7fffffff) idx = lo;             // nothing compared greater (NaN scores)
+}
+
+__global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
+                                  int groups, int keep, int group_top, float weight_eps,
+                                  int* __restrict__ ids, float* __restrict__ weights) {
+    rv_pdl_prologue();
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + wib;
+    if (t >= n_tokens) return;
+    float* sc = smem + (size_t)wib * (E + groups);       // [E] scores, then [groups]
+    float* gs = sc + E;
+    for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-logits[(size_t)t * E + e]));
+    __syncwarp();
+    if (groups > 1) {
+        const int size = E / groups;
+        for (int g = 0; g < groups; ++g) {
+            // the sum of the group's largest scores: take them out one by one, then put them back
+            float sum = 0.f, taken_v[MOE_MAX_GROUP_TOP];
+            int taken_i[MOE_MAX_GROUP_TOP];
+            const int n_take = min(group_top, size);
+            for (int k = 0; k < n_take; ++k) {
+                float v;
+                int i;
+                moe_warp_argmax(sc, g * size, (g + 1) * size, lane, v, i);
+                sum += v;
+                taken_v[k] = v;
+                taken_i[k] = i;
+                __syncwarp();
+                if (lane == 0) sc[i] = -INFINITY;
+                __syncwarp();
+            }
+            if (lane == 0) {
+                for (int k = 0; k < n_take; ++k) sc[taken_i[k]] = taken_v[k];
+                gs[g] = sum;
+            }
+            __syncwarp();
+        }
+        // the `keep` best groups stay: their score becomes +inf, then the others' experts go
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY;
+            int idx = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = gs[g];
+                if (v != INFINITY && v > best) {
+                    best = v;
+                    idx = g;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+                if (ov > best || (ov == best && oi < idx)) {
+                    best = ov;
+                    idx = oi;
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && idx < groups) gs[idx] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / size] != INFINITY) sc[e] = -1.f;          // below every sigmoid
+        __syncwarp();
+    }
+    float sum = 0.f, mine = 0.f;
+    int mine_id = 0;
+    for (int k = 0; k < top; ++k) {
+        float v;
+        int i;
+        moe_warp_argmax(sc, 0, E, lane, v, i);
+        sum += v;
+        if (lane == (k & 31) && k < 32) {
+            mine = v;
+            mine_id = i;
+        }
+        if (k >= 32 && lane == 0) {                  // more than 32 experts a token: written at once
+            ids[(size_t)t * top + k] = i;
+            weights[(size_t)t * top + k] = v;        // divided below
+        }
+        __syncwarp();
+        if (lane == 0) sc[i] = -2.f;
+        __syncwarp();
+    }
+    const float inv = 1.f / (sum + weight_eps);
+    if (lane < top) {
+        ids[(size_t)t * top + lane] = mine_id;
+        weights[(size_t)t * top + lane] = mine * inv;
+    }
+    if (lane == 0)
+        for (int k = 32; k < top; ++k) weights[(size_t)t * top + k] *= inv;
+}
+
+// ---------------------------------------------------------------------------------
+#define MOE_ROWS 32        // output rows per block of the two simple kernels
+
+template <typename T>
+__global__ void moe_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ ids,
+                                   const T* __restrict__ gate_up, T* __restrict__ act, int top,
+                                   int E, int W, int F) {
+    rv_pdl_prologue();
+    extern __shared__ float xs[];                      // [W]
+    const int pair = blockIdx.x;
+    const int t = pair / top;
+    const int e = ids[pair];
+    for (int i = threadIdx.x; i < W; i += blockDim.x) xs[i] = rv_load(x + (size_t)t * W + i);
+    __syncthreads();
+    if (e < 0 || e >= E) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const T* wg = gate_up + (size_t)e * 2 * F * W;
+    const T* wu = wg + (size_t)F * W;
+    const int f_end = min(F, (int)(blockIdx.y + 1) * MOE_ROWS);
+    for (int f = blockIdx.y * MOE_ROWS + warp; f < f_end; f += nwarps) {
+        const T* g_row = wg + (size_t)f * W;
+        const T* u_row = wu + (size_t)f * W;
+        float g = 0.f, u = 0.f;
+        for (int i = lane; i < W; i += 32) {
+            const float xv = xs[i];
+            g += xv * rv_load(g_row + i);
+            u += xv * rv_load(u_row + i);
+        }
+        g = rv_warp_sum(g);
+        u = rv_warp_sum(u);
+        if (lane == 0) rv_store(act + (size_t)pair * F + f, g / (1.f + expf(-g)) * u);
+    }
+}
+
+template <typename T>
+__global__ void moe_down_kernel(const T* __restrict__ act, const int* __restrict__ ids,
+                                const float* __restrict__ weights, const T* __restrict__ down,
+                                T* __restrict__ out, int top, int E, int W, int F) {
+    rv_pdl_prologue();
+    extern __shared__ float as[];                      // [top * F]
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < top * F; i += blockDim.x)
+        as[i] = rv_load(act + (size_t)t * top * F + i);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int w_end = min(W, (int)(blockIdx.y + 1) * MOE_ROWS);
+    for (int w = blockIdx.y * MOE_ROWS + warp; w < w_end; w += nwarps) {
+        float y = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int e = ids[(size_t)t * top + k];
+            if (e < 0 || e >= E) continue;
+            const T* row = down + ((size_t)e * W + w) * F;
+            float s = 0.f;
+            for (int i = lane; i < F; i += 32) s += as[k * F + i] * rv_load(row + i);
+            s = rv_warp_sum(s);
+            y += weights[(size_t)t * top + k] * s;
+        }
+        if (lane == 0) rv_store(out + (size_t)t * W + w, y);
+    }
+}
+
+extern "C" int rv_moe_select(const float* logits, int n_tokens, int E, int top, int groups,
+                             int keep, int group_top, float weight_eps, int* ids, float* weights,
+                             void* stream) {
+    if (n_tokens == 0) return 0;
+    if (n_tokens < 0 || E < 1 || top < 1 || top > E) RV_FAIL("moe_select: bad sizes");
+    if (groups < 1 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < top)
+        RV_FAIL("moe_select: %d experts in %d groups of which %d are kept cannot give %d", E,
+                groups, keep, top);
+    if (group_top < 1 || group_top > MOE_MAX_GROUP_TOP)
+        RV_FAIL("moe_select: a group's score sums 1 to %d scores", MOE_MAX_GROUP_TOP);
+    const int wpb = 4;
+    const size_t smem = (size_t)wpb * (E + groups) * sizeof(float);
+    if (smem > 48 * 1024) RV_FAIL("moe_select: too many experts");
+    rv_launch(moe_select_kernel, dim3((n_tokens + wpb - 1) / wpb), dim3(wpb * 32), smem,
+              (cudaStream_t)stream, logits, n_tokens, E, top, groups, keep, group_top, weight_eps,
+              ids, weights);
+    RV_CHECK_LAUNCH("moe_select");
+    return 0;
+}
+
+// act: scratch [n_tokens * top, F] of the storage type.
+extern "C" int rv_moe_experts_simple(const void* x, int dtype, const int* ids, const float* weights,
+                                     const void* gate_up, const void* down, void* act, void* out,
+                                     int n_tokens, int top, int E, int W, int F, void* stream) {
+    if (n_tokens == 0) return 0;
+    if (n_tokens < 0 || top < 1 || E < 1 || W < 1 || F < 1) RV_FAIL("moe_experts: bad sizes");
+    if ((size_t)W * 4 > 200 * 1024 || (size_t)top * F * 4 > 200 * 1024)
+        RV_FAIL("moe_experts: rows of %d or %d x %d values do not fit shared memory", W, top, F);
+    if ((long long)n_tokens * top > 0x7fffffffLL) RV_FAIL("moe_experts: too many rows");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem1 = (size_t)W * 4, smem2 = (size_t)top * F * 4;
+    RV_DISPATCH_DTYPE(dtype, "moe_experts", {
+        if (smem1 > 48 * 1024)
+            cudaFuncSetAttribute(moe_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem1);
+        if (smem2 > 48 * 1024)
+            cudaFuncSetAttribute(moe_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem2);
+        rv_launch(moe_gate_up_kernel<T>, dim3(n_tokens * top, (F + MOE_ROWS - 1) / MOE_ROWS),
+                  dim3(128), smem1, s, (const T*)x, ids, (const T*)gate_up, (T*)act, top, E, W, F);
+        rv_launch(moe_down_kernel<T>, dim3(n_tokens, (W + MOE_ROWS - 1) / MOE_ROWS), dim3(128),
+                  smem2, s, (const T*)act, ids, weights, (const T*)down, (T*)out, top, E, W, F);
+    });
+    RV_CHECK_LAUNCH("moe_experts");
+    return 0;
+}

@@ -457,11 +457,24 @@ class CudaOps:
         return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
-                        ctx, group, scale, window, out):
+                        ctx, group, scale, window, out, sinks=None, v_head_dim=None):
+        """`sinks` float32 [heads]: one more term exp(sinks[h]) in head h's softmax denominator;
+        `v_head_dim`: the size of a value head when it is not `head_dim`."""
         self._need(qkv, "query rows")
         self._need(out, "attention output", qkv.dtype)
         self._need(k_cache, "key pages", qkv.dtype)
         self._need(v_cache, "value pages", qkv.dtype)
+        vd = v_head_dim or head_dim
+        if sinks is not None:
+            self._need(sinks, "sinks", torch.float32)
+            if sinks.shape[0] != num_heads:
+                raise KernelError("paged_attention: one sink per query head")
+        if out.shape[1] != num_heads * vd:
+            raise KernelError("paged_attention: output width and head sizes disagree")
+        if sinks is not None or vd != head_dim:
+            return self._paged_attention_options(qkv, num_heads, num_kv_heads, head_dim, vd,
+                                                 k_cache, v_cache, ctx, group, scale, window, out,
+                                                 sinks)
         code = _code(qkv.dtype)
         win = c_int(window if window else 0)
         nd = ctx.n_decode
@@ -498,6 +511,35 @@ class CudaOps:
                 _ptr(ctx.ctx_lens), _ptr(ctx.token_req), _ptr(out), c_int(nd),
                 c_int(ctx.n_tokens - nd), c_int(num_heads), c_int(num_kv_heads),
                 c_int(head_dim), c_int(group.page_size), c_float(scale), win,
+                self._stream()), "paged_attention")
+
+    def _paged_attention_options(self, qkv, num_heads, num_kv_heads, head_dim, vd, k_cache,
+                                 v_cache, ctx, group, scale, window, out, sinks):
+        """Attention with sinks or a value size of its own: single tokens on the split kernel
+        with its merge, portions on the one-warp-per-(token, head) kernel, both in float32
+        arithmetic."""
+        nd = ctx.n_decode
+        code = _code(qkv.dtype)
+        win = c_int(window if window else 0)
+        if nd > 0:
+            need = self.lib.rv_paged_attention_decode_scratch_bytes(
+                c_int(nd), c_int(num_heads), c_int(vd), c_int(ctx.max_ctx_len))
+            scratch = self._scratch_buffer(need, qkv.device)
+            self._check(self.lib.rv_paged_attention_decode_ex(
+                _ptr(qkv), code, c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
+                _ptr(group.block_table), c_int(group.block_table.shape[1]), _ptr(ctx.ctx_lens),
+                _ptr(out), _ptr(scratch), c_longlong(scratch.numel()), c_int(nd),
+                c_int(ctx.max_ctx_len), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+                c_int(group.page_size), c_float(scale), win, c_int(vd), _ptr(sinks),
+                self._stream()), "paged_attention_decode")
+            self.launches += 1
+        if ctx.n_tokens > nd:
+            self._check(self.lib.rv_paged_attention_warp_ex(
+                _ptr(qkv), code, c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
+                _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
+                _ptr(ctx.ctx_lens), _ptr(ctx.token_req), _ptr(out), c_int(nd),
+                c_int(ctx.n_tokens - nd), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+                c_int(group.page_size), c_float(scale), win, c_int(vd), _ptr(sinks),
                 self._stream()), "paged_attention")
 
     def paged_attention_decode(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
@@ -819,6 +861,94 @@ class CudaOps:
             getattr(lib, f"rv_attention_mixed_mma_last_error_d{tag}").restype = ctypes.c_char_p
             self._attn_libs[key] = lib
         return lib
+
+    # ---- unit norm of q and k, query temperature, cache write ---------------------------
+
+    def qk_unit_write(self, rows, num_heads, num_kv_heads, head_dim, v_head_dim, eps, q_temp,
+                      positions, slot_mapping, k_cache, v_cache):
+        """`eps` None: no norm; `q_temp` = (coef, every) or None."""
+        self._need(rows, "q|k|v rows")
+        if k_cache is not None:
+            self._need(k_cache, "key pages", rows.dtype)
+            self._need(v_cache, "value pages", rows.dtype)
+        coef, every = q_temp if q_temp is not None else (0.0, 0)
+        self._check(self.lib.rv_qk_unit_write(
+            _ptr(rows), _code(rows.dtype), c_int(rows.shape[1]), c_int(rows.shape[0]),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(v_head_dim),
+            c_int(0 if eps is None else 1), c_float(eps or 0.0), c_float(coef), c_int(every),
+            _ptr(positions), _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), self._stream()),
+            "qk_unit_write")
+
+    # ---- latent rows: norm and cache write; the gate on the heads -------------------------
+
+    def latent_norm_write(self, rows, offset, rank, weight, eps, slot_mapping, cache):
+        self._need(rows, "q|gate|latent rows")
+        self._need(weight, "latent norm weight", torch.float32)
+        self._need(cache, "latent pages", rows.dtype)
+        if weight.shape[0] != rank or cache.shape[-1] * cache.shape[-2] != rank:
+            raise KernelError("latent_norm_write: the rank and the pages disagree")
+        self._check(self.lib.rv_latent_norm_write(
+            _ptr(rows), _code(rows.dtype), c_int(rows.shape[1]), c_int(rows.shape[0]),
+            c_int(offset), c_int(rank), _ptr(weight), c_float(eps), _ptr(slot_mapping),
+            _ptr(cache), self._stream()), "latent_norm_write")
+
+    def sigmoid_gate(self, x, rows, gate_off):
+        self._need(x, "heads to gate")
+        self._need(rows, "rows with the gate", x.dtype)
+        self._check(self.lib.rv_sigmoid_gate(
+            _ptr(x), _code(x.dtype), c_int(x.shape[0]), c_int(x.shape[1]), _ptr(rows),
+            c_int(rows.shape[1]), c_int(gate_off), self._stream()), "sigmoid_gate")
+
+    def heads_product(self, rows, offset, heads, size, w, out):
+        """out[n, h, :] = rows[n, offset + h * size : + size] . w[h] for w [heads, size, b]: one
+        small product per head, as one batched library product straight from and into the
+        [tokens, heads * size] layouts (a head is a batch entry whose rows are strided)."""
+        n = rows.shape[0]
+        b = w.shape[2]
+        if n == 0:
+            return
+        x = rows.as_strided((heads, n, size), (size, rows.stride(0), 1),
+                            rows.storage_offset() + offset)
+        y = out.as_strided((heads, n, b), (b, out.stride(0), 1), out.storage_offset())
+        if x.dtype != w.dtype:
+            x = x.to(w.dtype)
+        torch.bmm(x, w, out=y)
+        self.launches += 1
+
+    # ---- mixture of experts ---------------------------------------------------------------
+
+    def moe_select(self, logits, groups, keep, group_top, weight_eps, ids, weights):
+        self._need(logits, "router logits", torch.float32)
+        self._need(ids, "expert ids", torch.int32)
+        self._need(weights, "expert weights", torch.float32)
+        n, experts = logits.shape
+        self._check(self.lib.rv_moe_select(
+            _ptr(logits), c_int(n), c_int(experts), c_int(ids.shape[1]), c_int(groups),
+            c_int(keep), c_int(group_top), c_float(weight_eps), _ptr(ids), _ptr(weights),
+            self._stream()), "moe_select")
+
+    def moe_experts(self, x, ids, weights, gate_up, down, out):
+        """out[t] = sum_k weights[t, k] * down[e](silu(gate[e] x_t) * up[e] x_t), e = ids[t, k];
+        gate_up [E, 2F, W] (gate rows, then up rows), down [E, W, F]."""
+        self._need(x, "feed-forward input")
+        self._need(gate_up, "experts' gate and up matrices", x.dtype)
+        self._need(down, "experts' down matrices", x.dtype)
+        self._need(out, "feed-forward output", x.dtype)
+        n, top = ids.shape
+        experts, width, ffn = down.shape
+        if gate_up.shape != (experts, 2 * ffn, width) or x.shape[1] != width:
+            raise KernelError("moe_experts: shapes disagree")
+        act = torch.empty((n * top, ffn), dtype=x.dtype, device=x.device)
+        self._check(self.lib.rv_moe_experts_simple(
+            _ptr(x), _code(x.dtype), _ptr(ids), _ptr(weights), _ptr(gate_up), _ptr(down),
+            _ptr(act), _ptr(out), c_int(n), c_int(top), c_int(experts), c_int(width), c_int(ffn),
+            self._stream()), "moe_experts")
+        self.launches += 1
+
+    def softcap(self, logits, cap):
+        self._need(logits, "logits", torch.float32)
+        self._check(self.lib.rv_softcap(_ptr(logits), c_longlong(logits.numel()), c_float(cap),
+                                        self._stream()), "softcap")
 
     # ---- sampling --------------------------------------------------------------------
 
