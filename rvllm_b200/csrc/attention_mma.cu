@@ -169,7 +169,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
     const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ q_start, const int* __restrict__ ctx_lens, bf16* __restrict__ out,
     float* __restrict__ part_o, float2* __restrict__ part_ml, int max_splits, int first_req,
-    int num_heads, int num_kv_heads, int page_size, float scale_log2, int window) {
+    int num_heads, int num_kv_heads, int page_size, float scale_log2, int window,
+    const float* __restrict__ sinks) {
     rv_pdl_prologue();
     constexpr int BM = 16 * NWARPS;
     constexpr int LD = HD + 8;          // padded row: conflict-free ldmatrix for HD % 16 == 0
@@ -327,6 +328,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
         if (ok_a) {
             const int tok = row_a / G, hg = row_a - tok * G;
             bf16* dst = out + (size_t)(qs + tok) * num_heads * HD + (size_t)(g * G + hg) * HD + col;
+            // a sink: one more term exp(sink - max) in the denominator, with no value
+            if (sinks) l_a += exp2f(sinks[g * G + hg] * 1.4426950408889634f - m_a);
             const float inv = 1.f / l_a;
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i)
@@ -335,6 +338,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
         if (ok_b) {
             const int tok = row_b / G, hg = row_b - tok * G;
             bf16* dst = out + (size_t)(qs + tok) * num_heads * HD + (size_t)(g * G + hg) * HD + col;
+            if (sinks) l_b += exp2f(sinks[g * G + hg] * 1.4426950408889634f - m_b);
             const float inv = 1.f / l_b;
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i)
@@ -793,7 +797,7 @@ extern "C" int RV_SYM(rv_paged_attention_prefill_mma)(
     const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
     int max_blocks, const int* q_start, const int* ctx_lens, void* out, int first_req, int n_reqs,
     int max_q_len, int num_heads, int num_kv_heads, int page_size, float scale, int window,
-    void* stream) {
+    const float* sinks, void* stream) {
     if (n_reqs == 0) return 0;
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 ||
         max_q_len <= 0 || n_reqs < 0)
@@ -829,13 +833,13 @@ extern "C" int RV_SYM(rv_paged_attention_prefill_mma)(
                   (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
                   (const bf16*)v_cache, block_table, max_blocks, q_start, ctx_lens, (bf16*)out,
                   (float*)nullptr, (float2*)nullptr, 0, first_req, num_heads, num_kv_heads, page_size,
-                  scale * 1.4426950408889634f, window);
+                  scale * 1.4426950408889634f, window, sinks);
     else
         rv_launch(paged_attention_mma_kernel<RV_HD, 4, false>, dim3(grid), dim3(128), smem_bytes<4>(),
                   (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
                   (const bf16*)v_cache, block_table, max_blocks, q_start, ctx_lens, (bf16*)out,
                   (float*)nullptr, (float2*)nullptr, 0, first_req, num_heads, num_kv_heads, page_size,
-                  scale * 1.4426950408889634f, window);
+                  scale * 1.4426950408889634f, window, sinks);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(cudaGetErrorString(e));
     return 0;

@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(192, 3) paged_attention_prefill_tcgen05_kernel
     const int* __restrict__ q_start, const int* __restrict__ ctx_lens, bf16* __restrict__ out,
     int first_req, int num_heads, int num_kv_heads, int q_block, int page_size, float scale_log2,
     int window, int* __restrict__ status, int nsplit, float* __restrict__ part_o,
-    float2* __restrict__ part_ml) {
+    float2* __restrict__ part_ml, const float* __restrict__ sinks) {
     static_assert(HD == 64, "one 128-byte swizzle row per key");
     rv_pdl_prologue();
     // blocks are handed out in the order x, then y: with the key/value head in x, all heads of a
@@ -488,6 +488,9 @@ __global__ void __launch_bounds__(192, 3) paged_attention_prefill_tcgen05_kernel
                     }
                 }
             } else {
+            // a sink: one more term exp(sink - offset) in the denominator, with no value
+            if (sinks && row_ok)
+                l_run += at_exp2(sinks[g * G + head] * 1.4426950408889634f - m_run);
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             bf16* dst = out + (size_t)(qs + q0 + tok) * num_heads * HD + (size_t)(g * G + head) * HD;
 #pragma unroll
@@ -528,7 +531,8 @@ template <int HD>
 __global__ void __launch_bounds__(16 * (HD / 4)) paged_attention_prefill_merge_kernel(
     const float* __restrict__ part_o, const float2* __restrict__ part_ml,
     const int* __restrict__ q_start, const int* __restrict__ ctx_lens, bf16* __restrict__ out,
-    int first_req, int num_heads, int num_kv_heads, int q_block, int window, int nsplit) {
+    int first_req, int num_heads, int num_kv_heads, int q_block, int window, int nsplit,
+    const float* __restrict__ sinks) {
     rv_pdl_prologue();
     constexpr int CH = HD / 4;                                  // 4-column chunks of a row
     const int r_local = (int)blockIdx.z / (AT_ROWS / 16), rows0 = ((int)blockIdx.z % (AT_ROWS / 16)) * 16;
@@ -573,6 +577,7 @@ __global__ void __launch_bounds__(16 * (HD / 4)) paged_attention_prefill_merge_k
             o.x += v[p].x * w; o.y += v[p].y * w; o.z += v[p].z * w; o.w += v[p].w * w;
         }
     }
+    if (sinks && L > 0.f) L += at_exp2(sinks[g * G + head] * 1.4426950408889634f - M);   // once
     const float inv = L > 0.f ? 1.f / L : 0.f;
     bf16* dst = out + (size_t)(qs + q0 + tok) * num_heads * HD + (size_t)(g * G + head) * HD + c;
     const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * inv, o.y * inv);
@@ -658,7 +663,7 @@ extern "C" int AT_SYM(rv_paged_attention_prefill_tcgen05)(
     long long total_slots, const int* block_table, int max_blocks, const int* q_start,
     const int* ctx_lens, void* out, int first_req, int n_reqs, int max_q_len, int max_ctx_len,
     int num_heads, int num_kv_heads, int page_size, float scale, int window, int* status,
-    void* scratch, long long scratch_bytes, int n_sms, void* stream) {
+    void* scratch, long long scratch_bytes, int n_sms, const float* sinks, void* stream) {
     if (n_reqs == 0 || max_q_len == 0) return 0;
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || n_reqs < 0)
         return at_fail("paged_attention_prefill_tcgen05: bad head counts");
@@ -697,14 +702,15 @@ extern "C" int AT_SYM(rv_paged_attention_prefill_tcgen05)(
     rv_launch(paged_attention_prefill_tcgen05_kernel<RV_HD>, dim3(num_kv_heads, nqb, n_reqs * parts),
               dim3(192), smem, (cudaStream_t)stream, map_q, map_k, map_v, block_table, max_blocks,
               q_start, ctx_lens, (bf16*)out, first_req, num_heads, num_kv_heads, q_block, page_size,
-              scale * 1.4426950408889634f, window, status, parts, part_o, part_ml);
+              scale * 1.4426950408889634f, window, status, parts, part_o, part_ml, sinks);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return at_fail(cudaGetErrorString(e));
     if (parts > 1) {
         rv_launch(paged_attention_prefill_merge_kernel<RV_HD>,
                   dim3(num_kv_heads, nqb, n_reqs * (AT_ROWS / 16)), dim3(16 * (RV_HD / 4)), 0,
                   (cudaStream_t)stream, (const float*)part_o, (const float2*)part_ml,
-                  q_start, ctx_lens, (bf16*)out, first_req, num_heads, num_kv_heads, q_block, window, parts);
+                  q_start, ctx_lens, (bf16*)out, first_req, num_heads, num_kv_heads, q_block, window, parts,
+                  sinks);
         e = cudaGetLastError();
         if (e != cudaSuccess) return at_fail(cudaGetErrorString(e));
     }

@@ -9,7 +9,8 @@
 //                  largest allowed s are chosen (ties: the lower index first, for groups too);
 //                  weights = chosen s / (their sum + weight_eps).  One warp per token.
 //   moe_gate_up    act[pair, f] = silu(<gate_e[f], x_t>) * <up_e[f], x_t> for pair = t * top + k,
-//                  e = ids[t, k]; gate_up is [E, 2F, W] (gate rows, then up rows).
+//                  e = ids[t, k]; gate_up is [E, 2F, W] with gate and up rows alternating
+//                  (row 2f: gate f, row 2f + 1: up f).
 //   moe_down       out[t, w] = sum_k weights[t, k] * <down_e(k)[w], act[t * top + k]>, the sum in
 //                  the order of k; down is [E, W, F].
 // Dot products and the activation are float32; act is rounded to the storage type.
@@ -151,11 +152,10 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ x, const int* __restric
     if (e < 0 || e >= E) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const T* wg = gate_up + (size_t)e * 2 * F * W;
-    const T* wu = wg + (size_t)F * W;
     const int f_end = min(F, (int)(blockIdx.y + 1) * MOE_ROWS);
     for (int f = blockIdx.y * MOE_ROWS + warp; f < f_end; f += nwarps) {
-        const T* g_row = wg + (size_t)f * W;
-        const T* u_row = wu + (size_t)f * W;
+        const T* g_row = wg + (size_t)(2 * f) * W;
+        const T* u_row = g_row + W;
         float g = 0.f, u = 0.f;
         for (int i = lane; i < W; i += 32) {
             const float xv = xs[i];

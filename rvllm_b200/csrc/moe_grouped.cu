@@ -318,6 +318,7 @@ extern "C" int rv_moe_experts_grouped(const void* x, const int* ids, const float
         RV_FAIL("moe_experts_grouped: buffers must be 16-byte aligned (scratch 256)");
     const long long rows = rv_moe_grouped_rows((int)pairs, E, TN);
     const int max_tiles = (int)(rows / TN);
+    if (max_tiles > 65535) RV_FAIL("moe_experts_grouped: too many token tiles");
     int* sorted_token = (int*)scratch;
     int* pair_pos = sorted_token + rows;
     int* tile_expert = pair_pos + pairs;

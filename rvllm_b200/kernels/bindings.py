@@ -84,6 +84,13 @@ class CudaOps:
         # tokens, head size 64); "0": always the separate kernel
         self.fuse_qkv_rope = os.environ.get("RVLLM_FUSE_QKV_ROPE", "1") == "1"
         self._check(self.lib.rv_gemm_tcgen05_init(), "gemm_tcgen05 set-up")
+        self._check(self.lib.rv_moe_grouped_init(), "moe_grouped set-up")
+        self.lib.rv_moe_grouped_scratch_bytes.restype = c_longlong
+        # experts of a mixture: "grouped" = tokens sorted by expert through grouped tcgen05
+        # products (bfloat16, widths in multiples of 8), "simple" = token by token; "auto" =
+        # grouped from `moe_grouped_min` (token, expert) pairs on
+        self.moe_mode = os.environ.get("RVLLM_MOE", "auto")
+        self.moe_grouped_min = int(os.environ.get("RVLLM_MOE_GROUPED_MIN", "16"))
         # float32 products must be float32: no TF32, no reduced-precision accumulation
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
@@ -213,8 +220,8 @@ class CudaOps:
             if device is not None:
                 self._gemm_status(device).zero_()
             raise KernelError(f"a kernel gave up waiting on an mbarrier (code {code}: 1-4 "
-                              f"gemm_tcgen05, 12 decode attention, 21 prefill attention); its "
-                              f"output is not valid")
+                              f"gemm_tcgen05, 12 decode attention, 21 prefill attention, 31-34 "
+                              f"grouped experts); its output is not valid")
 
     def check_status(self) -> None:
         """Raise if a kernel recorded that one of its bounded waits ran out (this
@@ -412,7 +419,7 @@ class CudaOps:
                 and out.data_ptr() % 16 == 0)
 
     def paged_attention_prefill_tcgen05(self, qkv, num_heads, num_kv_heads, head_dim, k_cache,
-                                        v_cache, ctx, group, scale, window, out):
+                                        v_cache, ctx, group, scale, window, out, sinks=None):
         """Requests [n_decode, n_reqs) -- the ones that bring more than one token -- on the
         tcgen05 kernel (bfloat16, head size 64)."""
         lib = self._attn5_lib(head_dim)
@@ -432,7 +439,7 @@ class CudaOps:
                 c_int(num_heads), c_int(num_kv_heads), c_int(group.page_size), c_float(scale),
                 c_int(window if window else 0), _ptr(self._gemm_status(qkv.device)),
                 _ptr(scratch), c_longlong(scratch.numel() if scratch is not None else 0),
-                c_int(self._sm_count), self._stream())
+                c_int(self._sm_count), _ptr(sinks), self._stream())
         self.launches += 1
         if rc != 0:
             msg = getattr(lib, f"rv_attention_tcgen05_last_error_hd{head_dim}")().decode()
@@ -471,20 +478,26 @@ class CudaOps:
                 raise KernelError("paged_attention: one sink per query head")
         if out.shape[1] != num_heads * vd:
             raise KernelError("paged_attention: output width and head sizes disagree")
-        if sinks is not None or vd != head_dim:
+        mma = self._mma_ok(qkv.dtype, head_dim)
+        if vd != head_dim or (sinks is not None and not mma):
+            # a value size of its own, or sinks where no tensor-core kernel applies: the
+            # float32-arithmetic kernels
             return self._paged_attention_options(qkv, num_heads, num_kv_heads, head_dim, vd,
                                                  k_cache, v_cache, ctx, group, scale, window, out,
                                                  sinks)
         code = _code(qkv.dtype)
         win = c_int(window if window else 0)
         nd = ctx.n_decode
-        mma = self._mma_ok(qkv.dtype, head_dim)
         if nd > 0:
             if mma and self.decode_attention == "mma":
                 self.paged_attention_decode_mma(qkv, num_heads, num_kv_heads, head_dim, k_cache,
                                                 v_cache, group.block_table, ctx.q_start,
                                                 ctx.ctx_lens, nd, ctx.max_ctx_len,
-                                                group.page_size, scale, window, out)
+                                                group.page_size, scale, window, out, sinks=sinks)
+            elif sinks is not None:
+                self._paged_attention_options(qkv, num_heads, num_kv_heads, head_dim, vd, k_cache,
+                                              v_cache, ctx, group, scale, window, out, sinks,
+                                              prompts=False)
             else:
                 self.paged_attention_decode(qkv, num_heads, num_kv_heads, head_dim, k_cache,
                                             v_cache, group.block_table, ctx.ctx_lens, nd,
@@ -493,7 +506,8 @@ class CudaOps:
                 and self._tcgen05_prefill_ok(qkv, out, num_heads, num_kv_heads, head_dim,
                                              group.page_size)):
             self.paged_attention_prefill_tcgen05(qkv, num_heads, num_kv_heads, head_dim, k_cache,
-                                                 v_cache, ctx, group, scale, window, out)
+                                                 v_cache, ctx, group, scale, window, out,
+                                                 sinks=sinks)
         elif ctx.n_tokens > nd and mma and self.prefill_attention in ("auto", "mma", "tcgen05"):
             lib = self._attn_lib(head_dim)
             fn = getattr(lib, f"rv_paged_attention_prefill_mma_hd{head_dim}")
@@ -502,19 +516,19 @@ class CudaOps:
                 _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
                 _ptr(ctx.ctx_lens), _ptr(out), c_int(nd), c_int(ctx.n_reqs - nd),
                 c_int(ctx.max_q_len), c_int(num_heads), c_int(num_kv_heads),
-                c_int(group.page_size), c_float(scale), win, self._stream()),
+                c_int(group.page_size), c_float(scale), win, _ptr(sinks), self._stream()),
                 "paged_attention_prefill_mma")
         elif ctx.n_tokens > nd:
-            self._check(self.lib.rv_paged_attention_warp(
+            self._check(self.lib.rv_paged_attention_warp_ex(
                 _ptr(qkv), code, c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
                 _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
                 _ptr(ctx.ctx_lens), _ptr(ctx.token_req), _ptr(out), c_int(nd),
                 c_int(ctx.n_tokens - nd), c_int(num_heads), c_int(num_kv_heads),
-                c_int(head_dim), c_int(group.page_size), c_float(scale), win,
-                self._stream()), "paged_attention")
+                c_int(head_dim), c_int(group.page_size), c_float(scale), win, c_int(head_dim),
+                _ptr(sinks), self._stream()), "paged_attention")
 
     def _paged_attention_options(self, qkv, num_heads, num_kv_heads, head_dim, vd, k_cache,
-                                 v_cache, ctx, group, scale, window, out, sinks):
+                                 v_cache, ctx, group, scale, window, out, sinks, prompts=True):
         """Attention with sinks or a value size of its own: single tokens on the split kernel
         with its merge, portions on the one-warp-per-(token, head) kernel, both in float32
         arithmetic."""
@@ -533,7 +547,7 @@ class CudaOps:
                 c_int(group.page_size), c_float(scale), win, c_int(vd), _ptr(sinks),
                 self._stream()), "paged_attention_decode")
             self.launches += 1
-        if ctx.n_tokens > nd:
+        if ctx.n_tokens > nd and prompts:
             self._check(self.lib.rv_paged_attention_warp_ex(
                 _ptr(qkv), code, c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
                 _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
@@ -560,7 +574,7 @@ class CudaOps:
 
     def paged_attention_decode_mma(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
                                    block_table, q_start, ctx_lens, n_reqs, max_ctx_len,
-                                   page_size, scale, window, out, scratch=None):
+                                   page_size, scale, window, out, scratch=None, sinks=None):
         """Tensor-core split-KV attention (bfloat16) for requests [0, n_reqs) that bring one
         token each; the splits are combined by the merge kernel."""
         stream = (self.decode_kernel in ("stream", "auto") and head_dim == 64
@@ -592,10 +606,10 @@ class CudaOps:
                 c_float(scale), win, c_int(split), c_int(self._sm_count),
                 _ptr(self._gemm_status(qkv.device)), self._stream()),
                 "paged_attention_decode_stream")
-            self._check(self.lib.rv_paged_attention_merge(
+            self._check(self.lib.rv_paged_attention_merge_ex(
                 _ptr(scratch), _ptr(ctx_lens), _ptr(out), _code(out.dtype), c_int(n_reqs),
                 c_int(max_ctx_len), c_int(num_heads), c_int(head_dim), win, c_int(split),
-                self._stream()), "paged_attention_merge")
+                _ptr(sinks), self._stream()), "paged_attention_merge")
             return
         fn = getattr(lib, f"rv_paged_attention_decode_mma_hd{head_dim}")
         self._check_attn(lib, head_dim, fn(
@@ -604,10 +618,10 @@ class CudaOps:
             c_longlong(scratch.numel() * scratch.element_size()), c_int(n_reqs),
             c_int(max_ctx_len), c_int(num_heads), c_int(num_kv_heads), c_int(page_size),
             c_float(scale), win, c_int(split), self._stream()), "paged_attention_decode_mma")
-        self._check(self.lib.rv_paged_attention_merge(
+        self._check(self.lib.rv_paged_attention_merge_ex(
             _ptr(scratch), _ptr(ctx_lens), _ptr(out), _code(out.dtype), c_int(n_reqs),
             c_int(max_ctx_len), c_int(num_heads), c_int(head_dim), win, c_int(split),
-            self._stream()), "paged_attention_merge")
+            _ptr(sinks), self._stream()), "paged_attention_merge")
 
     def paged_attention_general(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
                                 ctx, group, scale, window, out):
@@ -938,6 +952,23 @@ class CudaOps:
         experts, width, ffn = down.shape
         if gate_up.shape != (experts, 2 * ffn, width) or x.shape[1] != width:
             raise KernelError("moe_experts: shapes disagree")
+        grouped = (x.dtype == torch.bfloat16 and width % 8 == 0 and ffn % 8 == 0
+                   and self.moe_mode != "simple"
+                   and (self.moe_mode == "grouped" or n * top >= self.moe_grouped_min))
+        if grouped:
+            # the token tile follows the rows an expert gets on average
+            avg = n * top / experts
+            tn = 16 if avg <= 8 else 32 if avg <= 24 else 64 if avg <= 48 else 128
+            need = int(self.lib.rv_moe_grouped_scratch_bytes(
+                c_int(n), c_int(top), c_int(experts), c_int(width), c_int(ffn), c_int(tn)))
+            scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+            self._check(self.lib.rv_moe_experts_grouped(
+                _ptr(x), _ptr(ids), _ptr(weights), _ptr(gate_up), _ptr(down), _ptr(out),
+                _ptr(scratch), c_longlong(need), _ptr(self._gemm_status(x.device)), c_int(n),
+                c_int(top), c_int(experts), c_int(width), c_int(ffn), c_int(tn), self._stream()),
+                "moe_experts_grouped")
+            self.launches += 4
+            return
         act = torch.empty((n * top, ffn), dtype=x.dtype, device=x.device)
         self._check(self.lib.rv_moe_experts_simple(
             _ptr(x), _code(x.dtype), _ptr(ids), _ptr(weights), _ptr(gate_up), _ptr(down),

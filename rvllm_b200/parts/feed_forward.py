@@ -94,7 +94,8 @@ class MoE(FeedForward):
         y       = sum_{e chosen} s_e / (sum_chosen s + weight_eps) * down_e(silu(gate_e x) * up_e x)
 
     The router matrix is kept in float32, so its product runs in float32 whatever the compute
-    type.  The experts' matrices are stacked ([experts, 2 ffn, hidden] gate over up, and
+    type.  The experts' matrices are stacked ([experts, 2 ffn, hidden] with gate and up rows
+    alternating, so that a pair lies in neighbouring rows of a product's tile, and
     [experts, hidden, ffn]); `ops.moe_experts` chooses between a kernel that walks each token's
     experts (few tokens) and grouped matrix products over the tokens sorted by expert.  A
     token's result is a sum over its own experts in the order they were chosen, so it does not
@@ -145,9 +146,10 @@ class MoE(FeedForward):
         self.router = tensors[n["router"]].to(torch.float32).contiguous()
         first = tensors[n[(0, "gate")]]
         self.gate_up = torch.stack([
-            torch.cat([tensors[n[(e, "gate")]].to(first.dtype),
-                       tensors[n[(e, "up")]].to(first.dtype)], dim=0)
-            for e in range(spec.experts)]).contiguous()                  # [E, 2F, W]
+            torch.stack([tensors[n[(e, "gate")]].to(first.dtype),
+                         tensors[n[(e, "up")]].to(first.dtype)], dim=1).reshape(
+                             2 * spec.ffn_dim, spec.hidden)
+            for e in range(spec.experts)]).contiguous()          # [E, 2F, W]: gate f, up f, ...
         self.down = torch.stack([tensors[n[(e, "down")]].to(first.dtype)
                                  for e in range(spec.experts)]).contiguous()   # [E, W, F]
 

@@ -346,8 +346,8 @@ class PlainOps:
         for t in range(n):
             for k in range(top):
                 e = int(ids[t, k])
-                gu = _f(gate_up[e]) @ _f(x[t])
-                act = (torch.nn.functional.silu(gu[:F]) * gu[F:]).to(x.dtype)
+                gu = _f(gate_up[e]) @ _f(x[t])               # gate and up rows alternate
+                act = (torch.nn.functional.silu(gu[0::2]) * gu[1::2]).to(x.dtype)
                 y[t] += float(weights[t, k]) * (_f(down[e]) @ _f(act))
         out.copy_(y.to(out.dtype))
 

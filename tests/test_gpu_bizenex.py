@@ -288,7 +288,7 @@ def test_moe_select(ops, shape):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(50, 34, 5, 2), (96, 64, 6, 2), (320, 96, 8, 4), (128, 256, 4, 1),
                                    (64, 48, 16, 16)])
-@pytest.mark.parametrize("n", [1, 3, 37, 300])
+@pytest.mark.parametrize("n", [1, 3, 37, 300, 1500])
 def test_moe_experts(ops, dtype, shape, n):
     W, F, E, top = shape
     g = torch.Generator().manual_seed(W + n)
@@ -307,7 +307,7 @@ def test_moe_experts(ops, dtype, shape, n):
     for t in range(n):
         for k in range(top):
             e = int(ids[t, k])
-            want[t] += float(wts[t, k]) * plain.expert(xs[t], gu[e, :F], gu[e, F:], dn[e])
+            want[t] += float(wts[t, k]) * plain.expert(xs[t], gu[e, 0::2], gu[e, 1::2], dn[e])
     close(out, want, dtype)
 
 
