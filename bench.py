@@ -33,6 +33,8 @@ steps it holds 4096 - K tokens, then K steps are timed with CUDA events and end 
              events recorded around it (`gpu_idle_frac`: the share of the run's wall time in
              which the device waited for the host)
 
+`--only bizenex` (not part of the default run) measures Bizenex (latent and grouped-query
+attention with sinks, a mixture of experts) beside an all-attention LFM2 of equal sizes.
 `--only retorax` (not part of the default run) measures another design, Retorax, beside LFM2
 at equal sizes (width 1024 and 2048, eight layers): a 2,048-token prompt, single tokens at
 batch 8 and 64, and the device time of every kernel of a step against its roofline.
@@ -847,6 +849,49 @@ def retorax_config(sz):
             "norm": {"eps": 1e-5}, "layers": layers}
 
 
+BIZENEX_SIZES = {
+    # latent and grouped-query attention in turn, every second latent layer reading the one
+    # before; `ff` is an expert's inner width, a token uses `top` of `experts`
+    "w1024": {"width": 1024, "layers": 8, "heads": 16, "kv": 4, "dim": 64, "rank": 128,
+              "experts": 16, "top": 4, "groups": (4, 2), "ff": 1024, "vocab": 32768},
+    "w2048": {"width": 2048, "layers": 8, "heads": 32, "kv": 8, "dim": 64, "rank": 128,
+              "experts": 16, "top": 4, "groups": (4, 2), "ff": 2048, "vocab": 32768},
+}
+
+
+def bizenex_config(sz):
+    layers, last = [], None
+    mlp = {"kind": "moe", "expert": {"ff": sz["ff"]},
+           "router": {"experts": sz["experts"], "top": sz["top"],
+                      "groups": {"count": sz["groups"][0], "keep": sz["groups"][1]}}}
+    for i in range(sz["layers"]):
+        if i % 2 == 0:
+            mixer = {"heads": sz["heads"], "dim": sz["dim"], "vdim": sz["dim"],
+                     "kv_rank": sz["rank"], "scale": sz["dim"] ** -0.5}
+            if last is not None and (i // 2) % 2 == 1:
+                mixer["kv_from"] = last
+            else:
+                last = i
+            layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+        else:
+            mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"],
+                     "scale": 12.0 / sz["dim"] ** 0.5, "q_temp": {"coef": 0.5, "every": 128}}
+            layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Bizenex", "vocab": sz["vocab"], "width": sz["width"],
+            "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": layers}
+
+
+def lfm2_all_attention(sz):
+    """LFM2 with the same width and layer count, attention in every layer with the same head
+    counts and sizes, and a SwiGLU as wide as the experts a token uses together."""
+    d = dict(LFM2_1_2B)
+    d.update(num_hidden_layers=sz["layers"], full_attn_idxs=list(range(sz["layers"])),
+             hidden_size=sz["width"], num_attention_heads=sz["heads"],
+             num_key_value_heads=sz["kv"], head_dim=sz["dim"], block_ff_dim=sz["top"] * sz["ff"],
+             block_auto_adjust_ff_dim=False, vocab_size=sz["vocab"], max_position_embeddings=8192)
+    return d
+
+
 def lfm2_like(sz):
     """LFM2 with the same width, layer count, attention places and head sizes, and a SwiGLU of
     as many parameters as the dense feed-forward (three matrices of 2/3 the inner width)."""
@@ -862,8 +907,9 @@ def lfm2_like(sz):
 class OpTimer:
     """Device time of each call of the kernel set's methods, by CUDA events around the call."""
     NAMES = ("embed", "add_rmsnorm", "add_layernorm", "linear", "linear_qk_norm_rope_write",
-             "rope_partial_write", "paged_attention", "paged_attention_mixed", "short_conv",
-             "mingru_scan", "swiglu", "xielu")
+             "qk_norm_rope_write", "rope_partial_write", "paged_attention", "paged_attention_mixed",
+             "short_conv", "mingru_scan", "swiglu", "xielu", "qk_unit_write", "latent_norm_write",
+             "heads_product", "sigmoid_gate", "moe_select", "moe_experts", "softcap")
 
     def __init__(self, torch, ops):
         self.torch, self.ops, self.events, self.saved = torch, ops, [], {}
@@ -899,10 +945,10 @@ class OpTimer:
         return {k: {"calls": v[0], "us": round(v[1], 1)} for k, v in out.items()}
 
 
-def run_designs(args):
-    """Retorax beside LFM2 at equal sizes (`--only retorax`): prompt and single-token
-    throughput, and the device time of every kernel of one prompt step and one single-token
-    step with its share of the roofline.  One JSON line."""
+def run_designs(args, which="retorax"):
+    """Retorax (`--only retorax`) or Bizenex (`--only bizenex`) beside LFM2 at equal sizes:
+    prompt and single-token throughput, and the device time of every kernel of one prompt step
+    and one single-token step with its share of the roofline.  One JSON line."""
     import torch
 
     from rvllm_b200.config import config_from_dict
@@ -910,14 +956,17 @@ def run_designs(args):
     from rvllm_b200.weights import write_random_model
 
     pk = peaks()
-    out = {"only": "retorax", "peaks": pk["source"], "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1)}
+    out = {"only": which, "peaks": pk["source"], "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1)}
     gen = torch.Generator().manual_seed(0)
     T, CTX = 2048, 1024
-    for size_name, sz in RETORAX_SIZES.items():
+    sizes = RETORAX_SIZES if which == "retorax" else BIZENEX_SIZES
+    for size_name, sz in sizes.items():
         if args.design_size not in ("all", size_name):
             continue
         entry = {}
-        for design, data in (("retorax", retorax_config(sz)), ("lfm2", lfm2_like(sz))):
+        pair = (("retorax", retorax_config(sz)), ("lfm2", lfm2_like(sz))) if which == "retorax" \
+            else (("bizenex", bizenex_config(sz)), ("lfm2", lfm2_all_attention(sz)))
+        for design, data in pair:
             cfg = config_from_dict(data)
             tmp = tempfile.mkdtemp(prefix="rvllm_bench_")
             try:
@@ -986,7 +1035,8 @@ def run_designs(args):
             entry[design] = res
             del model
             torch.cuda.empty_cache()
-        entry["rooflines"] = design_rooflines(sz, entry, pk, T, CTX)
+        entry["rooflines"] = design_rooflines(sz, entry, pk, T, CTX) if which == "retorax" \
+            else bizenex_rooflines(sz, entry, pk, T, CTX)
         out[size_name] = entry
     print(json.dumps(out))
     return 0
@@ -1040,6 +1090,54 @@ def design_rooflines(sz, entry, pk, T, CTX):
 
 
 
+def bizenex_rooflines(sz, entry, pk, T, CTX):
+    """Per kernel pair (Bizenex's kernel, LFM2's like kernel): device time of all calls in the
+    prompt step, and the time the roofline allows: bytes / measured copy rate for the elementwise
+    kernels, tensor FLOPs / measured GEMM rate for attention and for the matrix products."""
+    W, F, H, G, D, R = sz["width"], sz["ff"], sz["heads"], sz["kv"], sz["dim"], sz["rank"]
+    L, E, top, V = sz["layers"], sz["experts"], sz["top"], sz["vocab"]
+    hbm = pk["hbm_gbs"] * 1e3                       # bytes per microsecond
+    tens = pk["bf16_tflops"] * 1e6                  # FLOPs per microsecond
+    n_lat, n_att = (L + 1) // 2, L // 2
+    pairs = T * (T + 1) // 2                        # (query, key) pairs of a prompt
+    qkv_cols = (H + 2 * G) * D
+    ideal = {
+        "add_layernorm": (2 * L + 1) * T * W * (4 + 4 + 2 + 2) / hbm,
+        "add_rmsnorm": (2 * L + 1) * T * W * (4 + 4 + 2 + 2) / hbm,
+        # scores and values of every pair: latent heads of size R, grouped heads of size D
+        "paged_attention": (n_lat * pairs * 4.0 * H * R + n_att * pairs * 4.0 * H * D) / tens,
+        "paged_attention_lfm2": L * pairs * 4.0 * H * D / tens,
+        # q and k read and written, k and v written to the pages
+        "qk_unit_write": n_att * T * ((H + G) * D * 4 + 2 * G * D * 2) / hbm,
+        "qk_norm_rope_write": L * T * ((H + G) * D * 4 + 2 * G * D * 2) / hbm,
+        "latent_norm_write": (n_lat + 1) // 2 * T * R * 4 / hbm,
+        "sigmoid_gate": n_lat * T * H * D * 6 / hbm,
+        "moe_select": L * T * (E * 4 + top * 8) / hbm,
+        # the experts' three matrices for `top` experts a token, against the library's products
+        "moe_experts": L * T * top * 6.0 * F * W / tens,
+        "linear_lfm2": (L * T * 2.0 * W * (qkv_cols + H * D + 3 * top * F) + 2.0 * W * V) / tens,
+        "swiglu": L * T * top * F * 6 / hbm,
+        "heads_product": n_lat * T * 2.0 * H * (D * R + R * D) / tens,
+    }
+    ours, theirs = entry["bizenex"]["prefill_2048_kernels_us"], entry["lfm2"]["prefill_2048_kernels_us"]
+    like = (("add_layernorm", "add_rmsnorm", "add_rmsnorm"),
+            ("paged_attention", "paged_attention", "paged_attention_lfm2"),
+            ("qk_unit_write", "qk_norm_rope_write", "qk_norm_rope_write"),
+            ("latent_norm_write", "qk_norm_rope_write", "qk_norm_rope_write"),
+            ("sigmoid_gate", "swiglu", "swiglu"), ("moe_select", "swiglu", "swiglu"),
+            ("moe_experts", "linear", "linear_lfm2"), ("heads_product", "linear", "linear_lfm2"))
+    rows = {}
+    for mine, other, other_ideal in like:
+        a, b = ours.get(mine), theirs.get(other)
+        if a and b:
+            rows[mine] = {"us": a["us"], "roofline_us": round(ideal[mine], 1),
+                          "times_roofline": round(a["us"] / ideal[mine], 2),
+                          "like": other, "like_us": b["us"],
+                          "like_roofline_us": round(ideal[other_ideal], 1),
+                          "like_times_roofline": round(b["us"] / ideal[other_ideal], 2)}
+    return rows
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -1057,14 +1155,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", default="1.2b", choices=sorted(SIZES),
                     help="layer sizes: LFM2-1.2B (the default and the headline), 700M or 350M")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload", "further", "retorax"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload", "further", "retorax", "bizenex"],
                     help="run one part only (for profiling); the JSON line then lacks the rest")
     ap.add_argument("--workloads", default="both", choices=["both", "none"] + sorted(WORKLOADS),
                     help="scheduler workloads to add to the line (default: both)")
     ap.add_argument("--workload", default="350m-mixed", choices=sorted(WORKLOADS),
                     help="with --only workload: which one")
     ap.add_argument("--design-size", default="all", choices=["all"] + sorted(RETORAX_SIZES),
-                    help="with --only retorax: which of the sizes")
+                    help="with --only retorax or bizenex: which of the sizes")
     ap.add_argument("--kernel", default="all",
                     help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK, elementwise, copy_rate or all")
     ap.add_argument("--kernel-batch", type=int, default=64)
@@ -1089,6 +1187,8 @@ def main():
         return run_further(args)
     if args.only == "retorax":
         return run_designs(args)
+    if args.only == "bizenex":
+        return run_designs(args, "bizenex")
     if args.only == "workload":
         print(json.dumps({"only": "workload", args.workload: run_workload(args.workload)}))
         return 0

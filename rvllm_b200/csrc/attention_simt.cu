@@ -27,7 +27,7 @@
 // Plain reference: tests/plain_ops.py paged_attention.
 #include "common.cuh"
 
-#define RV_ATTN_MAX_DPL 8      // head_dim <= 256: up to 8 dimensions per lane
+#define RV_ATTN_MAX_DPL 16     // head sizes up to 512: up to 16 dimensions per lane
 #define RV_ATTN_GT 4           // query heads of a group handled together in decode
 #define RV_ATTN_SPLIT 256      // keys per decode split
 
@@ -366,7 +366,8 @@ static int check_attention_sizes(const char* name, int num_heads, int num_kv_hea
         case 3: { constexpr int DPL = 3; __VA_ARGS__; break; }            \
         case 4: { constexpr int DPL = 4; __VA_ARGS__; break; }            \
         case 5: case 6: { constexpr int DPL = 6; __VA_ARGS__; break; }    \
-        default: { constexpr int DPL = 8; __VA_ARGS__; break; }           \
+        case 7: case 8: { constexpr int DPL = 8; __VA_ARGS__; break; }    \
+        default: { constexpr int DPL = 16; __VA_ARGS__; break; }          \
     }
 
 // `vd`: size of a value head; `sinks`: float32 [num_heads] or null (see the top of the file).

@@ -137,6 +137,20 @@ def test_attention_with_sinks_against_plain(ops, dtype, sizes):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [(8, 2, 64, 64), (6, 1, 96, 96), (4, 4, 32, 32)])
+def test_short_portion_after_a_long_context(ops, dtype, sizes):
+    """A few tokens at the end of 1,500: the kernels that share a block's keys out over several
+    blocks and merge the parts count the sink once."""
+    H, G, d, dv = sizes
+    S = 1500
+    q, k, v, sink = _case(H, G, d, dv, S, 7, dtype)
+    sink = sink + 3.0                                              # a sink that matters
+    for first in (S - 64, S - 2):
+        want = plain_attend(q[first:].numpy(), k.numpy(), v.numpy(), 0.15, sink, first)
+        close(_attend(ops, q[first:], k, v, first, 16, dtype, 0.15, sink), want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(4, 2, 32, 16), (8, 2, 64, 64), (6, 1, 96, 96)])
 def test_attention_one_key_stands_out(ops, dtype, sizes):
     """Among 700 keys one is made to win: the first tokens, far back, on both sides of page
