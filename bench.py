@@ -909,7 +909,7 @@ class OpTimer:
     NAMES = ("embed", "add_rmsnorm", "add_layernorm", "linear", "linear_qk_norm_rope_write",
              "qk_norm_rope_write", "rope_partial_write", "paged_attention", "paged_attention_mixed",
              "short_conv", "mingru_scan", "swiglu", "xielu", "qk_unit_write", "latent_norm_write",
-             "heads_product", "sigmoid_gate", "moe_select", "moe_experts", "softcap")
+             "heads_product", "sigmoid_gate", "moe_select", "moe_route", "moe_experts", "softcap")
 
     def __init__(self, torch, ops):
         self.torch, self.ops, self.events, self.saved = torch, ops, [], {}
@@ -1045,7 +1045,7 @@ def run_designs(args, which="retorax"):
 def _block_tensors(block):
     for part in (block.mixer, block.feed_forward):
         for v in vars(part).values() if part is not None else ():
-            if hasattr(v, "element_size") and v.dim() == 2:
+            if hasattr(v, "element_size") and v.dim() >= 2:
                 yield v
 
 
@@ -1112,7 +1112,8 @@ def bizenex_rooflines(sz, entry, pk, T, CTX):
         "qk_norm_rope_write": L * T * ((H + G) * D * 4 + 2 * G * D * 2) / hbm,
         "latent_norm_write": (n_lat + 1) // 2 * T * R * 4 / hbm,
         "sigmoid_gate": n_lat * T * H * D * 6 / hbm,
-        "moe_select": L * T * (E * 4 + top * 8) / hbm,
+        # the rows read, ids and weights written
+        "moe_route": L * T * (W * 2 + top * 8) / hbm,
         # the experts' three matrices for `top` experts a token, against the library's products
         "moe_experts": L * T * top * 6.0 * F * W / tens,
         "linear_lfm2": (L * T * 2.0 * W * (qkv_cols + H * D + 3 * top * F) + 2.0 * W * V) / tens,
@@ -1124,7 +1125,7 @@ def bizenex_rooflines(sz, entry, pk, T, CTX):
             ("paged_attention", "paged_attention", "paged_attention_lfm2"),
             ("qk_unit_write", "qk_norm_rope_write", "qk_norm_rope_write"),
             ("latent_norm_write", "qk_norm_rope_write", "qk_norm_rope_write"),
-            ("sigmoid_gate", "swiglu", "swiglu"), ("moe_select", "swiglu", "swiglu"),
+            ("sigmoid_gate", "swiglu", "swiglu"), ("moe_route", "swiglu", "swiglu"),
             ("moe_experts", "linear", "linear_lfm2"), ("heads_product", "linear", "linear_lfm2"))
     rows = {}
     for mine, other, other_ideal in like:

@@ -47,6 +47,27 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ x, int width, const T* __res
     rv_store(x + i, rv_load(x + i) / (1.f + expf(-g)));
 }
 
+// eight bfloat16 values a thread, 16-byte accesses
+__global__ void sigmoid_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ x, int width8,
+                                           const __nv_bfloat16* __restrict__ rows, int row_stride,
+                                           int gate_off, long long total8) {
+    rv_pdl_prologue();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const long long n = i / width8;
+    const int c = (int)(i - n * width8) * 8;
+    uint4 xv = *(const uint4*)(x + i * 8);
+    const uint4 gv = *(const uint4*)(rows + n * row_stride + gate_off + c);
+    __nv_bfloat162* xp = (__nv_bfloat162*)&xv;
+    const __nv_bfloat162* gp = (const __nv_bfloat162*)&gv;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(xp[j]), g = __bfloat1622float2(gp[j]);
+        xp[j] = __floats2bfloat162_rn(a.x / (1.f + expf(-g.x)), a.y / (1.f + expf(-g.y)));
+    }
+    *(uint4*)(x + i * 8) = xv;
+}
+
 extern "C" int rv_latent_norm_write(const void* rows, int dtype, int row_stride, int n_tokens,
                                     int offset, int rank, const float* weight, float eps,
                                     const int* slot_mapping, void* cache, void* stream) {
@@ -69,6 +90,15 @@ extern "C" int rv_sigmoid_gate(void* x, int dtype, int n, int width, const void*
     if (n < 0 || width <= 0 || gate_off < 0 || row_stride < gate_off + width)
         RV_FAIL("sigmoid_gate: bad sizes");
     const long long total = (long long)n * width;
+    if (dtype == RV_DTYPE_BF16 && width % 8 == 0 && row_stride % 8 == 0 && gate_off % 8 == 0 &&
+        ((uintptr_t)x & 15) == 0 && ((uintptr_t)rows & 15) == 0) {
+        const long long total8 = total / 8;
+        rv_launch(sigmoid_gate_bf16x8_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0,
+                  (cudaStream_t)stream, (__nv_bfloat16*)x, width / 8, (const __nv_bfloat16*)rows,
+                  row_stride, gate_off, total8);
+        RV_CHECK_LAUNCH("sigmoid_gate");
+        return 0;
+    }
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7fffffffLL) RV_FAIL("sigmoid_gate: too many values");
     RV_DISPATCH_DTYPE(dtype, "sigmoid_gate",

@@ -8,6 +8,8 @@
 //                  s, and only experts of the `keep` best groups can be chosen; the `top`
 //                  largest allowed s are chosen (ties: the lower index first, for groups too);
 //                  weights = chosen s / (their sum + weight_eps).  One warp per token.
+//   moe_route      the router's product (x [N, W] of any type, router float32 [E, W]) and the same
+//                  choice in one kernel.
 //   moe_gate_up    act[pair, f] = silu(<gate_e[f], x_t>) * <up_e[f], x_t> for pair = t * top + k,
 //                  e = ids[t, k]; gate_up is [E, 2F, W] with gate and up rows alternating
 //                  (row 2f: gate f, row 2f + 1: up f).
@@ -43,17 +45,13 @@ __device__ __forceinline__ void moe_warp_argmax(const float* sc, int lo, int hi,
     if (idx == 0x7fffffff) idx = lo;             // nothing compared greater (NaN scores)
 }
 
-__global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
-                                  int groups, int keep, int group_top, float weight_eps,
-                                  int* __restrict__ ids, float* __restrict__ weights) {
-    rv_pdl_prologue();
-    extern __shared__ float smem[];
-    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    const int t = blockIdx.x * (blockDim.x >> 5) + wib;
-    if (t >= n_tokens) return;
-    float* sc = smem + (size_t)wib * (E + groups);       // [E] scores, then [groups]
-    float* gs = sc + E;
-    for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-logits[(size_t)t * E + e]));
+// One token's choice, by one warp.  sc [E]: router logits on entry (scores afterwards);
+// gs [groups]: scratch.  Writes ids[top] and weights[top].
+__device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int top, int groups,
+                                                int keep, int group_top, float weight_eps,
+                                                int* __restrict__ ids, float* __restrict__ weights,
+                                                int lane) {
+    for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
     __syncwarp();
     if (groups > 1) {
         const int size = E / groups;
@@ -119,8 +117,8 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens
             mine_id = i;
         }
         if (k >= 32 && lane == 0) {                  // more than 32 experts a token: written at once
-            ids[(size_t)t * top + k] = i;
-            weights[(size_t)t * top + k] = v;        // divided below
+            ids[k] = i;
+            weights[k] = v;                          // divided below
         }
         __syncwarp();
         if (lane == 0) sc[i] = -2.f;
@@ -128,11 +126,67 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens
     }
     const float inv = 1.f / (sum + weight_eps);
     if (lane < top) {
-        ids[(size_t)t * top + lane] = mine_id;
-        weights[(size_t)t * top + lane] = mine * inv;
+        ids[lane] = mine_id;
+        weights[lane] = mine * inv;
     }
     if (lane == 0)
-        for (int k = 32; k < top; ++k) weights[(size_t)t * top + k] *= inv;
+        for (int k = 32; k < top; ++k) weights[k] *= inv;
+}
+
+__global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
+                                  int groups, int keep, int group_top, float weight_eps,
+                                  int* __restrict__ ids, float* __restrict__ weights) {
+    rv_pdl_prologue();
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + wib;
+    if (t >= n_tokens) return;
+    float* sc = smem + (size_t)wib * (E + groups);       // [E] scores, then [groups]
+    for (int e = lane; e < E; e += 32) sc[e] = logits[(size_t)t * E + e];
+    __syncwarp();
+    moe_select_warp(sc, sc + E, E, top, groups, keep, group_top, weight_eps,
+                    ids + (size_t)t * top, weights + (size_t)t * top, lane);
+}
+
+// The router's product and the choice in one kernel: a block takes MOE_ROUTE_TOK tokens; each
+// warp walks the router's rows (float32) e = warp, warp + 8, ... and forms the logit of every
+// token of the block (so a row is read once per block, the tokens' rows come from L1), then
+// warp t makes token t's choice.  Products and sums are float32 whatever the rows' type.
+#define MOE_ROUTE_TOK 8
+template <typename T>
+__global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
+    const T* __restrict__ x, const float* __restrict__ router, int n_tokens, int W, int E, int top,
+    int groups, int keep, int group_top, float weight_eps, int* __restrict__ ids,
+    float* __restrict__ weights) {
+    rv_pdl_prologue();
+    extern __shared__ float smem[];                      // [MOE_ROUTE_TOK][E + groups]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t0 = blockIdx.x * MOE_ROUTE_TOK;
+    const int nt = min(MOE_ROUTE_TOK, n_tokens - t0);
+    const int stride = E + groups;
+    for (int e = warp; e < E; e += MOE_ROUTE_TOK) {
+        const float* w_row = router + (size_t)e * W;
+        float acc[MOE_ROUTE_TOK];
+#pragma unroll
+        for (int t = 0; t < MOE_ROUTE_TOK; ++t) acc[t] = 0.f;
+        for (int i = lane; i < W; i += 32) {
+            const float w = w_row[i];
+#pragma unroll
+            for (int t = 0; t < MOE_ROUTE_TOK; ++t)
+                if (t < nt) acc[t] += w * rv_load(x + (size_t)(t0 + t) * W + i);
+        }
+#pragma unroll
+        for (int t = 0; t < MOE_ROUTE_TOK; ++t) {
+            const float v = rv_warp_sum(acc[t]);
+            if (lane == 0) smem[t * stride + e] = v;
+        }
+    }
+    __syncthreads();
+    if (warp < nt) {
+        float* sc = smem + warp * stride;
+        moe_select_warp(sc, sc + E, E, top, groups, keep, group_top, weight_eps,
+                        ids + (size_t)(t0 + warp) * top, weights + (size_t)(t0 + warp) * top, lane);
+    }
 }
 
 // ---------------------------------------------------------------------------------
@@ -212,6 +266,27 @@ extern "C" int rv_moe_select(const float* logits, int n_tokens, int E, int top, 
               (cudaStream_t)stream, logits, n_tokens, E, top, groups, keep, group_top, weight_eps,
               ids, weights);
     RV_CHECK_LAUNCH("moe_select");
+    return 0;
+}
+
+extern "C" int rv_moe_route(const void* x, int dtype, const float* router, int n_tokens, int W,
+                            int E, int top, int groups, int keep, int group_top, float weight_eps,
+                            int* ids, float* weights, void* stream) {
+    if (n_tokens == 0) return 0;
+    if (n_tokens < 0 || W < 1 || E < 1 || top < 1 || top > E) RV_FAIL("moe_route: bad sizes");
+    if (groups < 1 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < top)
+        RV_FAIL("moe_route: %d experts in %d groups of which %d are kept cannot give %d", E, groups,
+                keep, top);
+    if (group_top < 1 || group_top > MOE_MAX_GROUP_TOP)
+        RV_FAIL("moe_route: a group's score sums 1 to %d scores", MOE_MAX_GROUP_TOP);
+    const size_t smem = (size_t)MOE_ROUTE_TOK * (E + groups) * sizeof(float);
+    if (smem > 48 * 1024) RV_FAIL("moe_route: too many experts");
+    const int blocks = (n_tokens + MOE_ROUTE_TOK - 1) / MOE_ROUTE_TOK;
+    RV_DISPATCH_DTYPE(dtype, "moe_route",
+                      (rv_launch(moe_route_kernel<T>, dim3(blocks), dim3(MOE_ROUTE_TOK * 32), smem,
+                                 (cudaStream_t)stream, (const T*)x, router, n_tokens, W, E, top,
+                                 groups, keep, group_top, weight_eps, ids, weights)));
+    RV_CHECK_LAUNCH("moe_route");
     return 0;
 }
 

@@ -30,7 +30,7 @@
 #define MG_BM 128
 #define MG_BK 64
 #define MG_MAX_STAGES 8
-#define MG_SMEM_LIMIT (200 * 1024)
+#define MG_SMEM_LIMIT (110 * 1024)     // two blocks an SM: one's epilogue beside the other's products
 
 __global__ void moe_sort_kernel(const int* __restrict__ ids, int P, int E, int top, int TN,
                                 int rows_pad, int max_tiles, int* __restrict__ sorted_token,
@@ -123,7 +123,7 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ ys, const int* __res
 
 // grid (ceil(n_out / 128), max_tiles); block 128 threads.
 template <bool SWIGLU>
-__global__ void __launch_bounds__(128) moe_grouped_kernel(
+__global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     bf16* __restrict__ out, int* __restrict__ status, const int* __restrict__ tile_expert,
     const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, int n_out, int kblocks,
@@ -226,22 +226,39 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(
     __syncthreads();          // the accumulator is complete, `failed` is final, copies are drained
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const bool good = !failed;
-    const int n = tile * MG_BM + warp * 32 + lane;            // this thread's row of W[e]
+    // The accumulator [128 rows of W x TN tokens] leaves through shared memory (the ring is free:
+    // every MMA that read it is done), turned to [token][column], so that the rows of the output
+    // are written in 16-byte pieces.  With SWIGLU a lane and its neighbour hold gate and up of
+    // one column, and half as many columns leave.
+    constexpr int CW = SWIGLU ? MG_BM / 2 : MG_BM;            // columns of the output per block
+    bf16* stage_out = (bf16*)base;                            // [TN][CW]
+    const int n_local = warp * 32 + lane;
     for (int c = 0; c < TN; c += 16) {
         unsigned r[16];
         tmem_load_16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c, r);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float v = good ? __uint_as_float(r[j]) : 0.f;
-            const size_t row = (size_t)(row0 + c + j);
             if (SWIGLU) {
                 const float other = __shfl_xor_sync(0xffffffffu, v, 1);    // the pair's up value
-                if (!(lane & 1) && n + 1 < n_out)
-                    out[row * (n_out >> 1) + (n >> 1)] =
+                if (!(lane & 1))
+                    stage_out[(c + j) * CW + (n_local >> 1)] =
                         __float2bfloat16_rn(v / (1.f + __expf(-v)) * other);
-            } else if (n < n_out) {
-                out[row * n_out + n] = __float2bfloat16_rn(v);
+            } else {
+                stage_out[(c + j) * CW + n_local] = __float2bfloat16_rn(v);
             }
+        }
+    }
+    __syncthreads();
+    {
+        const int out_cols = SWIGLU ? (n_out >> 1) : n_out;   // a multiple of 8
+        constexpr int CPR = CW / 8;                           // 16-byte pieces per row
+        for (int idx = tid; idx < TN * CPR; idx += 128) {
+            const int t = idx / CPR, ch = idx - t * CPR;
+            const int col = tile * CW + ch * 8;
+            if (col < out_cols)
+                *(uint4*)(out + (size_t)(row0 + t) * out_cols + col) =
+                    *(const uint4*)(stage_out + t * CW + ch * 8);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -278,7 +295,7 @@ static int grouped_product(const void* xs, const void* w, void* out, int* status
     const int per_stage = MG_BM * MG_BK * 2 + TN * MG_BK * 2;
     int stages = (MG_SMEM_LIMIT - 1024) / per_stage;
     if (stages > MG_MAX_STAGES) stages = MG_MAX_STAGES;
-    if (TN <= 32 && stages > 6) stages = 6;          // two blocks an SM when the token tile is small
+    if (stages > 6) stages = 6;
     const size_t smem = (size_t)stages * per_stage + 1024;
     dim3 grid((n_out + MG_BM - 1) / MG_BM, max_tiles);
     if (swiglu)

@@ -941,6 +941,21 @@ class CudaOps:
             c_int(keep), c_int(group_top), c_float(weight_eps), _ptr(ids), _ptr(weights),
             self._stream()), "moe_select")
 
+    def moe_route(self, x, router, groups, keep, group_top, weight_eps, ids, weights):
+        """The router's product (float32 `router` [experts, width], float32 sums) and the
+        choice of `moe_select`, in one kernel."""
+        self._need(x, "feed-forward input")
+        self._need(router, "router matrix", torch.float32)
+        self._need(ids, "expert ids", torch.int32)
+        self._need(weights, "expert weights", torch.float32)
+        experts, width = router.shape
+        if x.shape[1] != width:
+            raise KernelError("moe_route: widths disagree")
+        self._check(self.lib.rv_moe_route(
+            _ptr(x), _code(x.dtype), _ptr(router), c_int(x.shape[0]), c_int(width), c_int(experts),
+            c_int(ids.shape[1]), c_int(groups), c_int(keep), c_int(group_top), c_float(weight_eps),
+            _ptr(ids), _ptr(weights), self._stream()), "moe_route")
+
     def moe_experts(self, x, ids, weights, gate_up, down, out):
         """out[t] = sum_k weights[t, k] * down[e](silu(gate[e] x_t) * up[e] x_t), e = ids[t, k];
         gate_up [E, 2F, W] (gate rows, then up rows), down [E, W, F]."""

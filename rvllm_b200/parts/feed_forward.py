@@ -93,8 +93,8 @@ class MoE(FeedForward):
         chosen  = the `top` allowed experts with the largest s  (ties: the lower index)
         y       = sum_{e chosen} s_e / (sum_chosen s + weight_eps) * down_e(silu(gate_e x) * up_e x)
 
-    The router matrix is kept in float32, so its product runs in float32 whatever the compute
-    type.  The experts' matrices are stacked ([experts, 2 ffn, hidden] with gate and up rows
+    The router matrix is kept in float32 and its product is formed in float32 whatever the
+    compute type, in the kernel that also makes the choice (`ops.moe_route`).  The experts' matrices are stacked ([experts, 2 ffn, hidden] with gate and up rows
     alternating, so that a pair lies in neighbouring rows of a product's tile, and
     [experts, hidden, ffn]); `ops.moe_experts` chooses between a kernel that walks each token's
     experts (few tokens) and grouped matrix products over the tokens sorted by expert.  A
@@ -156,10 +156,11 @@ class MoE(FeedForward):
     def forward(self, normed, ctx):
         s = self.spec
         n = normed.shape[0]
-        logits = self.ops.linear(normed, self.router, out_dtype=torch.float32)
         ids = torch.empty((n, s.top), dtype=torch.int32, device=normed.device)
         weights = torch.empty((n, s.top), dtype=torch.float32, device=normed.device)
-        self.ops.moe_select(logits, s.groups, s.keep, s.group_top, s.weight_eps, ids, weights)
+        # the router's product and the choice: one kernel
+        self.ops.moe_route(normed, self.router, s.groups, s.keep, s.group_top, s.weight_eps,
+                           ids, weights)
         out = self.ops.new_rows(n, s.hidden, self.dtype, normed.device)
         self.ops.moe_experts(normed, ids, weights, self.gate_up, self.down, out)
         return out

@@ -339,6 +339,9 @@ class PlainOps:
             ids[t] = chosen.to(torch.int32)
             weights[t] = s[chosen] / (s[chosen].sum() + weight_eps)
 
+    def moe_route(self, x, router, groups, keep, group_top, weight_eps, ids, weights):
+        self.moe_select(_f(x) @ _f(router).t(), groups, keep, group_top, weight_eps, ids, weights)
+
     def moe_experts(self, x, ids, weights, gate_up, down, out):
         n, top = ids.shape
         F = down.shape[2]

@@ -300,6 +300,27 @@ def test_moe_select(ops, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(50, 5, 2, 5, 3), (96, 8, 4, 2, 1), (1024, 64, 6, 8, 3), (333, 9, 3, 1, 1)])
+def test_moe_route(ops, dtype, shape):
+    """The router's product and the choice in one kernel against the plain route on float64
+    logits of the same (rounded) rows; 1, 7, 8, 9 and 100 tokens."""
+    W, E, top, groups, keep = shape
+    g = torch.Generator().manual_seed(W + E)
+    router = torch.randn(E, W, generator=g) * W ** -0.5
+    for n in (1, 7, 8, 9, 100):
+        x = (torch.randn(n, W, generator=g) * 2).to(dtype)
+        ids = torch.empty(n, top, dtype=torch.int32, device="cuda")
+        wts = torch.empty(n, top, dtype=torch.float32, device="cuda")
+        ops.moe_route(dev(x), dev(router), groups, keep, 2, 1e-20, ids, wts)
+        ids, wts = ids.cpu(), wts.cpu()
+        z = x.double().numpy() @ router.double().numpy().T
+        for t in range(n):
+            chosen, weights = plain.route(plain.sigmoid(z[t]), top, groups, keep)
+            assert ids[t].tolist() == chosen.tolist(), (n, t)
+            assert np.allclose(wts[t].numpy(), weights, rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(50, 34, 5, 2), (96, 64, 6, 2), (320, 96, 8, 4), (128, 256, 4, 1),
                                    (64, 48, 16, 16)])
 @pytest.mark.parametrize("n", [1, 3, 37, 300, 1500])
@@ -471,3 +492,66 @@ def test_greedy_generation_through_the_entry_point(folders, name):
                  GenerateOptions(max_tokens=new, block_size=8, stop_tokens=[], num_blocks=16,
                                  prefill_chunk=20)):
         assert gen.complete_batch(prompts, opts) == want
+
+
+def test_command_line_and_trace_replay(folders, tmp_path):
+    """The design through the programs a user starts: `rvllm random-model` writes a folder from a
+    config.json, `rvllm cli` completes prompts of token ids, `bin/trace_run` replays steps from
+    standard input and writes logits that equal the plain implementation's."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(bz.config("B")))
+    folder = str(tmp_path / "model")
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "rvllm"), "random-model",
+                        "--config", str(cfg_path), "--seed", "5", "--out", folder],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    tensors = bz.read_tensors(folder)
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "rvllm"), "cli", "--model", folder,
+                        "--dtype", "float32", "--token-ids", "--prompt", " ".join(map(str, prompt)),
+                        "--max-tokens", "5", "--block-size", "8"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [int(t) for t in r.stdout.strip().splitlines()[0].split()]
+    ids = list(prompt)
+    for tok in got:                           # each token is the plain argmax at its place
+        row = bz.plain_logits(folder, "B", ids, tensors=tensors)[-1]
+        assert float(row.max() - row[tok]) < 1e-3 * float(row.abs().max())
+        ids.append(tok)
+    assert len(got) == 5
+    reqs = _requests("B", (70, 33, 90, 41, 12), 4)
+    steps = schedules.mixed(reqs, seed=2)
+    vocab = bz.config("B")["vocab"]
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        cmd = [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder,
+               "--dtype", dtype, "--out", str(out), "--max-tokens",
+               str(schedules.tokens_held(steps, 64))]
+        r = subprocess.run(cmd, input="\n".join(json.dumps(s) for s in steps) + "\n",
+                           capture_output=True, text=True, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [l for l in r.stdout.split("\n") if l.startswith("done")] == \
+            [f"done {s['step']}" for s in steps]
+        got, pos = {}, {k: 0 for k in reqs}
+        for s in steps:
+            arr = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab)
+            k = 0
+            for e in s["entries"]:
+                for w in e["want"]:
+                    got[(e["id"], pos[e["id"]] + w)] = torch.from_numpy(arr[k].copy())
+                    k += 1
+                pos[e["id"]] += len(e["tokens"])
+            assert k == arr.shape[0]
+        over, total = 0, 0
+        for rid, ids in reqs.items():
+            ref = bz.plain_logits(folder, "B", ids, tensors=tensors)
+            for p in range(len(ids)):
+                err = float((got[(rid, p)].double() - ref[p]).abs().max() / ref.abs().max())
+                total += 1
+                over += not err < BOUND[dtype]
+        assert over <= (0 if dtype == "float32" else 0.04 * total), (dtype, over, total)
