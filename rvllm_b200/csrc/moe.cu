@@ -153,6 +153,21 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens
 // token of the block (so a row is read once per block, the tokens' rows come from L1), then
 // warp t makes token t's choice.  Products and sums are float32 whatever the rows' type.
 #define MOE_ROUTE_TOK 8
+__device__ __forceinline__ void moe_load8(const float* p, float (&v)[8]) {
+    const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void moe_load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *(const uint4*)p;
+    const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        v[2 * j] = f.x;
+        v[2 * j + 1] = f.y;
+    }
+}
 template <typename T>
 __global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
     const T* __restrict__ x, const float* __restrict__ router, int n_tokens, int W, int E, int top,
@@ -164,16 +179,33 @@ __global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
     const int t0 = blockIdx.x * MOE_ROUTE_TOK;
     const int nt = min(MOE_ROUTE_TOK, n_tokens - t0);
     const int stride = E + groups;
+    // eight values a lane and step (16-byte loads of the rows, two of the router) when the width
+    // allows, so that a warp has a row's whole stretch in flight at once
+    const bool vec = W % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)router & 15) == 0;
     for (int e = warp; e < E; e += MOE_ROUTE_TOK) {
         const float* w_row = router + (size_t)e * W;
         float acc[MOE_ROUTE_TOK];
 #pragma unroll
         for (int t = 0; t < MOE_ROUTE_TOK; ++t) acc[t] = 0.f;
-        for (int i = lane; i < W; i += 32) {
-            const float w = w_row[i];
+        if (vec) {
+            for (int i = lane * 8; i < W; i += 256) {
+                const float4 w0 = *(const float4*)(w_row + i), w1 = *(const float4*)(w_row + i + 4);
+                float xv[MOE_ROUTE_TOK][8];
 #pragma unroll
-            for (int t = 0; t < MOE_ROUTE_TOK; ++t)
-                if (t < nt) acc[t] += w * rv_load(x + (size_t)(t0 + t) * W + i);
+                for (int t = 0; t < MOE_ROUTE_TOK; ++t)
+                    moe_load8(x + (size_t)(t0 + min(t, nt - 1)) * W + i, xv[t]);
+#pragma unroll
+                for (int t = 0; t < MOE_ROUTE_TOK; ++t)
+                    acc[t] += w0.x * xv[t][0] + w0.y * xv[t][1] + w0.z * xv[t][2] + w0.w * xv[t][3] +
+                              w1.x * xv[t][4] + w1.y * xv[t][5] + w1.z * xv[t][6] + w1.w * xv[t][7];
+            }
+        } else {
+            for (int i = lane; i < W; i += 32) {
+                const float w = w_row[i];
+#pragma unroll
+                for (int t = 0; t < MOE_ROUTE_TOK; ++t)
+                    if (t < nt) acc[t] += w * rv_load(x + (size_t)(t0 + t) * W + i);
+            }
         }
 #pragma unroll
         for (int t = 0; t < MOE_ROUTE_TOK; ++t) {
