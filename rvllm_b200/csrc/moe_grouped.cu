@@ -31,6 +31,7 @@
 #define MG_BK 64
 #define MG_MAX_STAGES 8
 #define MG_SMEM_LIMIT (110 * 1024)     // two blocks an SM: one's epilogue beside the other's products
+#define MG_SMEM_MAX (200 * 1024)
 
 __global__ void moe_sort_kernel(const int* __restrict__ ids, int P, int E, int top, int TN,
                                 int rows_pad, int max_tiles, int* __restrict__ sorted_token,
@@ -121,16 +122,20 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ ys, const int* __res
     }
 }
 
-// grid (ceil(n_out / 128), max_tiles); block 128 threads.
+// grid (ceil(n_out / (128 MT)), max_tiles); block 128 threads.  MT (1 or 2): how many tiles of
+// 128 rows of W a block multiplies with its token tile; with two, the tokens' tile is copied
+// once for twice the products (the kernel is bound by what an SM copies from L2: 32 KB per 64
+// of K with one tile, 48 KB for two), each with an accumulator of its own in TMEM.
 template <bool SWIGLU>
 __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     bf16* __restrict__ out, int* __restrict__ status, const int* __restrict__ tile_expert,
     const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, int n_out, int kblocks,
-    int TN, int stages) {
+    int TN, int stages, int MT) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int w_tile = MG_BM * MG_BK * 2, x_tile = TN * MG_BK * 2;
+    const int w_half = MG_BM * MG_BK * 2;                     // one tile of 128 rows of W
+    const int w_tile = MT * w_half, x_tile = TN * MG_BK * 2;
     unsigned char* w_tiles = base;
     unsigned char* x_tiles = base + stages * w_tile;
     __shared__ __align__(8) unsigned long long full_bar[MG_MAX_STAGES];
@@ -145,9 +150,9 @@ __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
     const int expert = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x;
-    const int w_row = expert * n_out + tile * MG_BM;
+    const int w_row = expert * n_out + tile * MT * MG_BM;
     unsigned tmem_cols = 32;
-    while ((int)tmem_cols < TN) tmem_cols <<= 1;
+    while ((int)tmem_cols < MT * TN) tmem_cols <<= 1;
 
     if (tid == 0) {
         failed = 0;
@@ -173,7 +178,9 @@ __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
         // ---- producer ------------------------------------------------------------------------
         auto load = [&](int s, int kb) {
             mbar_expect_tx(&full_bar[s], (unsigned)(w_tile + x_tile));
-            tma_load_2d(w_tiles + s * w_tile, &map_w, &full_bar[s], kb * MG_BK, w_row);
+            for (int m = 0; m < MT; ++m)
+                tma_load_2d(w_tiles + s * w_tile + m * w_half, &map_w, &full_bar[s], kb * MG_BK,
+                            w_row + m * MG_BM);
             tma_load_2d(x_tiles + s * x_tile, &map_x, &full_bar[s], kb * MG_BK, row0);
         };
         const int pre = min(kblocks, stages);
@@ -208,11 +215,14 @@ __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned long long a0 = smem_desc_sw128(w_tiles + s * w_tile);
             const unsigned long long b0 = smem_desc_sw128(x_tiles + s * x_tile);
+            for (int m = 0; m < MT; ++m) {
+                const unsigned long long a0 = smem_desc_sw128(w_tiles + s * w_tile + m * w_half);
 #pragma unroll
-            for (int k = 0; k < MG_BK / 16; ++k)
-                tcgen05_mma_f16(tmem_base, a0 + 2 * k, b0 + 2 * k, idesc, (i | k) != 0);
+                for (int k = 0; k < MG_BK / 16; ++k)
+                    tcgen05_mma_f16(tmem_base + (unsigned)(m * TN), a0 + 2 * k, b0 + 2 * k, idesc,
+                                    (i | k) != 0);
+            }
             tcgen05_commit(&empty_bar[s]);
         }
         tcgen05_commit(&accum_bar);
@@ -230,32 +240,33 @@ __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
     // every MMA that read it is done), turned to [token][column], so that the rows of the output
     // are written in 16-byte pieces.  With SWIGLU a lane and its neighbour hold gate and up of
     // one column, and half as many columns leave.
-    constexpr int CW = SWIGLU ? MG_BM / 2 : MG_BM;            // columns of the output per block
+    constexpr int CW = SWIGLU ? MG_BM / 2 : MG_BM;            // columns of the output per tile of W
     bf16* stage_out = (bf16*)base;                            // [TN][CW]
     const int n_local = warp * 32 + lane;
-    for (int c = 0; c < TN; c += 16) {
-        unsigned r[16];
-        tmem_load_16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c, r);
+    const int out_cols = SWIGLU ? (n_out >> 1) : n_out;       // a multiple of 8
+    constexpr int CPR = CW / 8;                               // 16-byte pieces per row
+    for (int m = 0; m < MT; ++m) {
+        if (m > 0) __syncthreads();                           // the staged tile has left
+        for (int c = 0; c < TN; c += 16) {
+            unsigned r[16];
+            tmem_load_16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(m * TN + c), r);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float v = good ? __uint_as_float(r[j]) : 0.f;
-            if (SWIGLU) {
-                const float other = __shfl_xor_sync(0xffffffffu, v, 1);    // the pair's up value
-                if (!(lane & 1))
-                    stage_out[(c + j) * CW + (n_local >> 1)] =
-                        __float2bfloat16_rn(v / (1.f + __expf(-v)) * other);
-            } else {
-                stage_out[(c + j) * CW + n_local] = __float2bfloat16_rn(v);
+            for (int j = 0; j < 16; ++j) {
+                const float v = good ? __uint_as_float(r[j]) : 0.f;
+                if (SWIGLU) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v, 1);    // the pair's up value
+                    if (!(lane & 1))
+                        stage_out[(c + j) * CW + (n_local >> 1)] =
+                            __float2bfloat16_rn(v / (1.f + __expf(-v)) * other);
+                } else {
+                    stage_out[(c + j) * CW + n_local] = __float2bfloat16_rn(v);
+                }
             }
         }
-    }
-    __syncthreads();
-    {
-        const int out_cols = SWIGLU ? (n_out >> 1) : n_out;   // a multiple of 8
-        constexpr int CPR = CW / 8;                           // 16-byte pieces per row
+        __syncthreads();
         for (int idx = tid; idx < TN * CPR; idx += 128) {
             const int t = idx / CPR, ch = idx - t * CPR;
-            const int col = tile * CW + ch * 8;
+            const int col = (tile * MT + m) * CW + ch * 8;
             if (col < out_cols)
                 *(uint4*)(out + (size_t)(row0 + t) * out_cols + col) =
                     *(const uint4*)(stage_out + t * CW + ch * 8);
@@ -276,10 +287,10 @@ extern "C" long long rv_moe_grouped_rows(int pairs, int E, int TN) {
 
 extern "C" int rv_moe_grouped_init() {
     cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_LIMIT);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_MAX);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(moe_grouped_kernel<false>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_LIMIT);
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_MAX);
     if (e != cudaSuccess) RV_FAIL("moe_grouped: %s", cudaGetErrorString(e));
     if (!encode_fn()) RV_FAIL("moe_grouped: cuTensorMapEncodeTiled is not available in this driver");
     return 0;
@@ -292,18 +303,24 @@ static int grouped_product(const void* xs, const void* w, void* out, int* status
     if (make_map(&map_w, w, (long long)E * n_out, K, MG_BM)) return 1;
     if (make_map(&map_x, xs, rows, K, TN)) return 1;
     const int kblocks = (K + MG_BK - 1) / MG_BK;
-    const int per_stage = MG_BM * MG_BK * 2 + TN * MG_BK * 2;
-    int stages = (MG_SMEM_LIMIT - 1024) / per_stage;
-    if (stages > MG_MAX_STAGES) stages = MG_MAX_STAGES;
+    // two tiles of W a block where there are many tokens an expert and rows of W enough
+    // (RVLLM_MOE_MT=1 or 2 forces it)
+    static int forced_mt = getenv("RVLLM_MOE_MT") ? atoi(getenv("RVLLM_MOE_MT")) : 0;
+    int MT = (TN >= 128 && n_out >= 4 * MG_BM) ? 2 : 1;
+    if (forced_mt == 1 || forced_mt == 2) MT = forced_mt;
+    static int smem_limit = getenv("RVLLM_MOE_SMEM_KB") ? atoi(getenv("RVLLM_MOE_SMEM_KB")) * 1024 : MG_SMEM_LIMIT;
+    const int per_stage = MT * MG_BM * MG_BK * 2 + TN * MG_BK * 2;
+    int stages = (smem_limit - 1024) / per_stage;
     if (stages > 6) stages = 6;
+    if (stages < 2) stages = 2;
     const size_t smem = (size_t)stages * per_stage + 1024;
-    dim3 grid((n_out + MG_BM - 1) / MG_BM, max_tiles);
+    dim3 grid((n_out + MT * MG_BM - 1) / (MT * MG_BM), max_tiles);
     if (swiglu)
         rv_launch(moe_grouped_kernel<true>, grid, dim3(128), smem, stream, map_w, map_x, (bf16*)out,
-                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages);
+                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages, MT);
     else
         rv_launch(moe_grouped_kernel<false>, grid, dim3(128), smem, stream, map_w, map_x, (bf16*)out,
-                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages);
+                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages, MT);
     RV_CHECK_LAUNCH("moe_grouped");
     return 0;
 }

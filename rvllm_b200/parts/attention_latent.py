@@ -111,9 +111,8 @@ class LatentAttention(Mixer):
                                  mixed, sinks=self.sinks)
         # and out of it: [n, H, R] x [H, R, dv] -> [n, H, dv]
         out = self.ops.new_rows(n, H * dv, self.dtype, normed.device)
-        self.ops.heads_product(mixed, 0, H, R, self.w_uv_t, out)
-        if s.out_gate:
-            self.ops.sigmoid_gate(out, rows, gate_off)
+        self.ops.heads_product(mixed, 0, H, R, self.w_uv_t, out,
+                               gate_rows=rows if s.out_gate else None, gate_off=gate_off)
         return self.ops.linear(out, self.w_out, out_dtype=self.dtype)
 
 

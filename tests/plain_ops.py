@@ -312,10 +312,12 @@ class PlainOps:
                 pages[s] = c[t].to(pages.dtype)
 
     # ---- one small product per head -------------------------------------------------------
-    def heads_product(self, rows, offset, heads, size, w, out):
+    def heads_product(self, rows, offset, heads, size, w, out, gate_rows=None, gate_off=-1):
         x = _f(rows[:, offset:offset + heads * size]).reshape(-1, heads, size)
-        y = torch.einsum("nha,hab->nhb", x, _f(w))
-        out.copy_(y.reshape(out.shape).to(out.dtype))
+        y = torch.einsum("nha,hab->nhb", x, _f(w)).reshape(out.shape)
+        if gate_rows is not None:
+            y = y * torch.sigmoid(_f(gate_rows[:, gate_off:gate_off + out.shape[1]]))
+        out.copy_(y.to(out.dtype))
 
     def sigmoid_gate(self, x, rows, gate_off):
         g = torch.sigmoid(_f(rows[:, gate_off:gate_off + x.shape[1]]))

@@ -259,8 +259,11 @@ def test_latent_norm_write(ops, dtype, rank):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_heads_product_and_gate(ops, dtype):
+    """Few tokens (this library's kernel) and many (the batched library product), with the gate
+    in the same call and as a kernel of its own."""
     g = torch.Generator().manual_seed(3)
-    for n, H, a, b, offset in ((7, 3, 10, 6, 4), (130, 6, 32, 96, 0), (1, 8, 96, 80, 16)):
+    for n, H, a, b, offset in ((7, 3, 10, 6, 4), (130, 6, 32, 96, 0), (1, 8, 96, 80, 16), (64, 5, 24, 200, 8),
+                               (65, 2, 128, 64, 0), (9, 4, 512, 40, 0)):
         rows = torch.randn(n, offset + H * a + 9, generator=g).to(dtype)
         w = (torch.randn(H, a, b, generator=g) * 0.3).to(dtype)
         out = ops.new_rows(n, H * b, dtype, "cuda")
@@ -269,6 +272,9 @@ def test_heads_product_and_gate(ops, dtype):
         want = torch.einsum("nha,hab->nhb", x, w.double()).reshape(n, H * b)
         close(out, want, dtype)
         gate_rows = (torch.randn(n, 5 + H * b, generator=g) * 3).to(dtype)
+        gated = want * torch.sigmoid(gate_rows[:, 5:].double())
+        ops.heads_product(dev(rows), offset, H, a, dev(w), out, gate_rows=dev(gate_rows), gate_off=5)
+        close(out, gated, dtype)
         y = dev(want.to(dtype))
         ops.sigmoid_gate(y, dev(gate_rows), 5)
         close(y, want.to(dtype).double() * torch.sigmoid(gate_rows[:, 5:].double()), dtype)
@@ -322,7 +328,7 @@ def test_moe_route(ops, dtype, shape):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(50, 34, 5, 2), (96, 64, 6, 2), (320, 96, 8, 4), (128, 256, 4, 1),
-                                   (64, 48, 16, 16)])
+                                   (64, 48, 16, 16), (512, 264, 4, 2)])
 @pytest.mark.parametrize("n", [1, 3, 37, 300, 1500])
 def test_moe_experts(ops, dtype, shape, n):
     W, F, E, top = shape
