@@ -196,11 +196,12 @@ def test_sink_takes_weight(ops, dtype):
 # ---- unit norm, query temperature, cache write ------------------------------------------------
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(5, 2, 24, 40), (3, 3, 64, 16), (4, 1, 10, 6), (2, 0, 16, 8)])
+@pytest.mark.parametrize("sizes", [(5, 2, 24, 40), (3, 3, 64, 16), (4, 1, 10, 6), (2, 0, 16, 8),
+                                   (6, 2, 64, 64), (3, 1, 8, 8), (5, 5, 256, 256), (7, 0, 32, 32)])
 def test_qk_unit_write(ops, dtype, sizes):
     H, G, d, dv = sizes
     g = torch.Generator().manual_seed(H * 100 + d)
-    extra = 5
+    extra = 5 if (H + G) % 2 else 8        # rows that 16-byte accesses do and do not divide
     every = 7
     # positions on both sides of a temperature step: p + 1 = every - 1, every, every + 1, ...
     pos = torch.tensor([0, 1, 5, 6, 7, 12, 13, 14, 700, 69999, 4], dtype=torch.int32)
