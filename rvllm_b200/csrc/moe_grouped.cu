@@ -241,7 +241,8 @@ __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
     // are written in 16-byte pieces.  With SWIGLU a lane and its neighbour hold gate and up of
     // one column, and half as many columns leave.
     constexpr int CW = SWIGLU ? MG_BM / 2 : MG_BM;            // columns of the output per tile of W
-    bf16* stage_out = (bf16*)base;                            // [TN][CW]
+    constexpr int SW = CW + 8;                                // a staged row: padded against bank conflicts
+    bf16* stage_out = (bf16*)base;                            // [TN][SW]
     const int n_local = warp * 32 + lane;
     const int out_cols = SWIGLU ? (n_out >> 1) : n_out;       // a multiple of 8
     constexpr int CPR = CW / 8;                               // 16-byte pieces per row
@@ -250,17 +251,27 @@ __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
         for (int c = 0; c < TN; c += 16) {
             unsigned r[16];
             tmem_load_16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(m * TN + c), r);
+            if (SWIGLU) {
+                // An even lane holds the gate sums of its column, its neighbour the up sums.  For
+                // a pair of tokens the two lanes swap one value each way, so that the even lane
+                // has token j's pair and the odd lane token j + 1's: half the arithmetic a lane.
+                // The quotient is rounded to bfloat16, so the fast exponential and division do.
+                const bool odd = lane & 1;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float v = good ? __uint_as_float(r[j]) : 0.f;
-                if (SWIGLU) {
-                    const float other = __shfl_xor_sync(0xffffffffu, v, 1);    // the pair's up value
-                    if (!(lane & 1))
-                        stage_out[(c + j) * CW + (n_local >> 1)] =
-                            __float2bfloat16_rn(v / (1.f + __expf(-v)) * other);
-                } else {
-                    stage_out[(c + j) * CW + n_local] = __float2bfloat16_rn(v);
+                for (int j = 0; j < 16; j += 2) {
+                    const float mine0 = good ? __uint_as_float(r[j]) : 0.f;
+                    const float mine1 = good ? __uint_as_float(r[j + 1]) : 0.f;
+                    const float got = __shfl_xor_sync(0xffffffffu, odd ? mine0 : mine1, 1);
+                    const float g = odd ? got : mine0;         // odd: the gate of token j + 1
+                    const float u = odd ? mine1 : got;         // even: the up value of token j
+                    stage_out[(c + j + (odd ? 1 : 0)) * SW + (n_local >> 1)] =
+                        __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
                 }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    stage_out[(c + j) * SW + n_local] =
+                        __float2bfloat16_rn(good ? __uint_as_float(r[j]) : 0.f);
             }
         }
         __syncthreads();
@@ -269,7 +280,7 @@ __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
             const int col = (tile * MT + m) * CW + ch * 8;
             if (col < out_cols)
                 *(uint4*)(out + (size_t)(row0 + t) * out_cols + col) =
-                    *(const uint4*)(stage_out + t * CW + ch * 8);
+                    *(const uint4*)(stage_out + t * SW + ch * 8);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
