@@ -172,39 +172,57 @@ template <typename T>
 __global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
     const T* __restrict__ x, const float* __restrict__ router, int n_tokens, int W, int E, int top,
     int groups, int keep, int group_top, float weight_eps, int* __restrict__ ids,
-    float* __restrict__ weights) {
+    float* __restrict__ weights, int stage_rows) {
     rv_pdl_prologue();
-    extern __shared__ float smem[];                      // [MOE_ROUTE_TOK][E + groups]
+    extern __shared__ __align__(16) float smem[];        // [MOE_ROUTE_TOK][E + groups], then the rows
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t0 = blockIdx.x * MOE_ROUTE_TOK;
     const int nt = min(MOE_ROUTE_TOK, n_tokens - t0);
     const int stride = E + groups;
-    // eight values a lane and step (16-byte loads of the rows, two of the router) when the width
-    // allows, so that a warp has a row's whole stretch in flight at once
+    // eight values a lane and step (16-byte loads) when the width allows
     const bool vec = W % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)router & 15) == 0;
+    // The block's rows go to shared memory first (one round trip for all of them), so that the
+    // loop over a router row waits only for that row, whose loads the compiler can then issue
+    // several steps ahead.  Rows beyond the last token are zeros.
+    T* xs = (T*)(smem + ((MOE_ROUTE_TOK * stride + 3) & ~3));
+    const T* rows = x + (size_t)t0 * W;
+    if (stage_rows) {
+        if (vec) {
+            const int ppr = W * (int)sizeof(T) / 16;          // 16-byte pieces per row
+            const uint4* src = (const uint4*)rows;
+            for (int i = threadIdx.x; i < MOE_ROUTE_TOK * ppr; i += blockDim.x)
+                ((uint4*)xs)[i] = i / ppr < nt ? src[i] : make_uint4(0, 0, 0, 0);
+        } else {
+            for (int i = threadIdx.x; i < MOE_ROUTE_TOK * W; i += blockDim.x)
+                xs[i] = i / W < nt ? rows[i] : T(0.f);
+        }
+        __syncthreads();
+        rows = xs;
+    }
+    const int last = stage_rows ? MOE_ROUTE_TOK - 1 : nt - 1;   // staged rows are all there
     for (int e = warp; e < E; e += MOE_ROUTE_TOK) {
         const float* w_row = router + (size_t)e * W;
         float acc[MOE_ROUTE_TOK];
 #pragma unroll
         for (int t = 0; t < MOE_ROUTE_TOK; ++t) acc[t] = 0.f;
         if (vec) {
+#pragma unroll 4
             for (int i = lane * 8; i < W; i += 256) {
                 const float4 w0 = *(const float4*)(w_row + i), w1 = *(const float4*)(w_row + i + 4);
-                float xv[MOE_ROUTE_TOK][8];
 #pragma unroll
-                for (int t = 0; t < MOE_ROUTE_TOK; ++t)
-                    moe_load8(x + (size_t)(t0 + min(t, nt - 1)) * W + i, xv[t]);
-#pragma unroll
-                for (int t = 0; t < MOE_ROUTE_TOK; ++t)
-                    acc[t] += w0.x * xv[t][0] + w0.y * xv[t][1] + w0.z * xv[t][2] + w0.w * xv[t][3] +
-                              w1.x * xv[t][4] + w1.y * xv[t][5] + w1.z * xv[t][6] + w1.w * xv[t][7];
+                for (int t = 0; t < MOE_ROUTE_TOK; ++t) {
+                    float xv[8];
+                    moe_load8(rows + (size_t)min(t, last) * W + i, xv);
+                    acc[t] += w0.x * xv[0] + w0.y * xv[1] + w0.z * xv[2] + w0.w * xv[3] +
+                              w1.x * xv[4] + w1.y * xv[5] + w1.z * xv[6] + w1.w * xv[7];
+                }
             }
         } else {
             for (int i = lane; i < W; i += 32) {
                 const float w = w_row[i];
 #pragma unroll
                 for (int t = 0; t < MOE_ROUTE_TOK; ++t)
-                    if (t < nt) acc[t] += w * rv_load(x + (size_t)(t0 + t) * W + i);
+                    if (t <= last) acc[t] += w * rv_load(rows + (size_t)t * W + i);
             }
         }
 #pragma unroll
@@ -311,13 +329,17 @@ extern "C" int rv_moe_route(const void* x, int dtype, const float* router, int n
                 keep, top);
     if (group_top < 1 || group_top > MOE_MAX_GROUP_TOP)
         RV_FAIL("moe_route: a group's score sums 1 to %d scores", MOE_MAX_GROUP_TOP);
-    const size_t smem = (size_t)MOE_ROUTE_TOK * (E + groups) * sizeof(float);
-    if (smem > 48 * 1024) RV_FAIL("moe_route: too many experts");
+    size_t smem = (size_t)((MOE_ROUTE_TOK * (E + groups) + 3) & ~3) * sizeof(float);
+    if (smem > 40 * 1024) RV_FAIL("moe_route: too many experts");
+    // the block's rows in shared memory when they fit beside the logits in 48 KB
+    const size_t row_bytes = (size_t)MOE_ROUTE_TOK * W * (dtype == RV_DTYPE_BF16 ? 2 : 4);
+    const int stage_rows = smem + row_bytes <= 48 * 1024;
+    if (stage_rows) smem += row_bytes;
     const int blocks = (n_tokens + MOE_ROUTE_TOK - 1) / MOE_ROUTE_TOK;
     RV_DISPATCH_DTYPE(dtype, "moe_route",
                       (rv_launch(moe_route_kernel<T>, dim3(blocks), dim3(MOE_ROUTE_TOK * 32), smem,
                                  (cudaStream_t)stream, (const T*)x, router, n_tokens, W, E, top,
-                                 groups, keep, group_top, weight_eps, ids, weights)));
+                                 groups, keep, group_top, weight_eps, ids, weights, stage_rows)));
     RV_CHECK_LAUNCH("moe_route");
     return 0;
 }
