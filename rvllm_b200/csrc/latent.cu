@@ -136,6 +136,8 @@ __global__ void __launch_bounds__(128) heads_product_kernel(
         float acc[HP_TOK];
 #pragma unroll
         for (int t = 0; t < HP_TOK; ++t) acc[t] = 0.f;
+        // sixteen rows of w requested at a time: the loop waits for memory, not for arithmetic
+#pragma unroll 16
         for (int k = 0; k < a; ++k) {
             const float wv = rv_load(wh + (size_t)k * b + j);
 #pragma unroll

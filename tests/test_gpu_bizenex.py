@@ -307,7 +307,8 @@ def test_moe_select(ops, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(50, 5, 2, 5, 3), (96, 8, 4, 2, 1), (1024, 64, 6, 8, 3), (333, 9, 3, 1, 1)])
+@pytest.mark.parametrize("shape", [(50, 5, 2, 5, 3), (96, 8, 4, 2, 1), (1024, 64, 6, 8, 3), (333, 9, 3, 1, 1),
+                                   (256, 128, 8, 8, 4), (4000, 16, 4, 4, 2)])
 def test_moe_route(ops, dtype, shape):
     """The router's product and the choice in one kernel against the plain route on float64
     logits of the same (rounded) rows; 1, 7, 8, 9 and 100 tokens."""
