@@ -109,73 +109,3 @@ extern "C" int rv_sigmoid_gate(void* x, int dtype, int n, int width, const void*
     return 0;
 }
 
-// ---------------------------------------------------------------------------------
-// One small product per head for few tokens:
-//   out[n, h, j] = sum_i rows[n, offset + h * a + i] * w[h, i, j]     (w [H, a, b], float32 sums)
-// and, with gate_off >= 0, times sigmoid(gate_rows[n, gate_off + h * b + j]).  A block takes
-// HP_TOK tokens of one head; a thread owns output columns j = tid, tid + 128, ..., reads w's
-// rows coalesced and the tokens' values from shared memory.  Many tokens go to the library's
-// batched product instead (bindings.py heads_product).
-#define HP_TOK 8
-template <typename T>
-__global__ void __launch_bounds__(128) heads_product_kernel(
-    const T* __restrict__ rows, int row_stride, int offset, int n_tokens, int a, int b,
-    const T* __restrict__ w, T* __restrict__ out, int out_stride, const T* __restrict__ gate_rows,
-    int gate_stride, int gate_off) {
-    rv_pdl_prologue();
-    extern __shared__ float xs[];                        // [HP_TOK][a]
-    const int h = blockIdx.x, t0 = blockIdx.y * HP_TOK;
-    const int nt = min(HP_TOK, n_tokens - t0);
-    for (int i = threadIdx.x; i < HP_TOK * a; i += blockDim.x) {
-        const int t = i / a, k = i - t * a;
-        xs[i] = t < nt ? rv_load(rows + (size_t)(t0 + t) * row_stride + offset + (size_t)h * a + k) : 0.f;
-    }
-    __syncthreads();
-    const T* wh = w + (size_t)h * a * b;
-    for (int j = threadIdx.x; j < b; j += blockDim.x) {
-        float acc[HP_TOK];
-#pragma unroll
-        for (int t = 0; t < HP_TOK; ++t) acc[t] = 0.f;
-        // sixteen rows of w requested at a time: the loop waits for memory, not for arithmetic
-#pragma unroll 16
-        for (int k = 0; k < a; ++k) {
-            const float wv = rv_load(wh + (size_t)k * b + j);
-#pragma unroll
-            for (int t = 0; t < HP_TOK; ++t) acc[t] += xs[t * a + k] * wv;
-        }
-#pragma unroll
-        for (int t = 0; t < HP_TOK; ++t) {
-            if (t < nt) {
-                float v = acc[t];
-                if (gate_off >= 0) {
-                    const float g = rv_load(gate_rows + (size_t)(t0 + t) * gate_stride + gate_off +
-                                            (size_t)h * b + j);
-                    v = v / (1.f + expf(-g));
-                }
-                rv_store(out + (size_t)(t0 + t) * out_stride + (size_t)h * b + j, v);
-            }
-        }
-    }
-}
-
-extern "C" int rv_heads_product(const void* rows, int dtype, int row_stride, int offset, int n_tokens,
-                                int H, int a, int b, const void* w, void* out, int out_stride,
-                                const void* gate_rows, int gate_stride, int gate_off, void* stream) {
-    if (n_tokens == 0) return 0;
-    if (n_tokens < 0 || H < 1 || a < 1 || b < 1 || offset < 0 || row_stride < offset + H * a ||
-        out_stride < H * b)
-        RV_FAIL("heads_product: bad sizes");
-    if (gate_off >= 0 && (!gate_rows || gate_stride < gate_off + H * b))
-        RV_FAIL("heads_product: the gate's rows are too short");
-    const size_t smem = (size_t)HP_TOK * a * sizeof(float);
-    if (smem > 48 * 1024) RV_FAIL("heads_product: heads of %d values are too large", a);
-    const int tiles = (n_tokens + HP_TOK - 1) / HP_TOK;
-    if (tiles > 65535) RV_FAIL("heads_product: too many tokens for this kernel");
-    RV_DISPATCH_DTYPE(dtype, "heads_product",
-                      (rv_launch(heads_product_kernel<T>, dim3(H, tiles), dim3(128), smem,
-                                 (cudaStream_t)stream, (const T*)rows, row_stride, offset, n_tokens, a,
-                                 b, (const T*)w, (T*)out, out_stride, (const T*)gate_rows, gate_stride,
-                                 gate_off)));
-    RV_CHECK_LAUNCH("heads_product");
-    return 0;
-}

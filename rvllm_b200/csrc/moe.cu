@@ -133,67 +133,6 @@ __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int
         for (int k = 32; k < top; ++k) weights[k] *= inv;
 }
 
-// The same choice by one thread, for few experts: no shuffles, no meetings of the warp; the
-// same order of comparisons (a later expert or group wins only when strictly greater).
-__device__ __forceinline__ void moe_select_serial(float* sc, float* gs, int E, int top, int groups,
-                                                  int keep, int group_top, float weight_eps,
-                                                  int* __restrict__ ids, float* __restrict__ weights) {
-    for (int e = 0; e < E; ++e) sc[e] = 1.f / (1.f + expf(-sc[e]));
-    if (groups > 1) {
-        const int size = E / groups;
-        const int n_take = min(group_top, size);
-        for (int g = 0; g < groups; ++g) {
-            int taken[MOE_MAX_GROUP_TOP];
-            float sum = 0.f;
-            for (int k = 0; k < n_take; ++k) {
-                float best = -INFINITY;
-                int bi = g * size;
-                for (int e = g * size; e < (g + 1) * size; ++e) {
-                    bool used = false;
-                    for (int q = 0; q < k; ++q) used |= taken[q] == e;
-                    if (!used && sc[e] > best) {
-                        best = sc[e];
-                        bi = e;
-                    }
-                }
-                taken[k] = bi;
-                sum += best;
-            }
-            gs[g] = sum;
-        }
-        for (int k = 0; k < keep; ++k) {
-            float best = -INFINITY;
-            int bi = -1;
-            for (int g = 0; g < groups; ++g)
-                if (gs[g] != INFINITY && gs[g] > best) {
-                    best = gs[g];
-                    bi = g;
-                }
-            if (bi >= 0) gs[bi] = INFINITY;
-        }
-        for (int e = 0; e < E; ++e)
-            if (gs[e / size] != INFINITY) sc[e] = -1.f;
-    }
-    float sum = 0.f;
-    for (int k = 0; k < top; ++k) {
-        float best = -INFINITY;
-        int bi = 0;
-        for (int e = 0; e < E; ++e)
-            if (sc[e] > best) {
-                best = sc[e];
-                bi = e;
-            }
-        ids[k] = bi;
-        weights[k] = best;
-        sum += best;
-        sc[bi] = -2.f;
-    }
-    const float inv = 1.f / (sum + weight_eps);
-    for (int k = 0; k < top; ++k) weights[k] *= inv;
-}
-
-#define MOE_SERIAL_MAX_E 64
-
 __global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
                                   int groups, int keep, int group_top, float weight_eps,
                                   int* __restrict__ ids, float* __restrict__ weights) {
@@ -297,14 +236,8 @@ __global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
         float* sc = smem + warp * stride;
         int* my_ids = ids + (size_t)(t0 + warp) * top;
         float* my_weights = weights + (size_t)(t0 + warp) * top;
-        if (E <= MOE_SERIAL_MAX_E) {
-            if (lane == 0)
-                moe_select_serial(sc, sc + E, E, top, groups, keep, group_top, weight_eps, my_ids,
-                                  my_weights);
-        } else {
-            moe_select_warp(sc, sc + E, E, top, groups, keep, group_top, weight_eps, my_ids,
-                            my_weights, lane);
-        }
+        moe_select_warp(sc, sc + E, E, top, groups, keep, group_top, weight_eps, my_ids, my_weights,
+                        lane);
     }
 }
 

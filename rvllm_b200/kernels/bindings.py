@@ -89,9 +89,6 @@ class CudaOps:
         # experts of a mixture: "grouped" = tokens sorted by expert through grouped tcgen05
         # products (bfloat16, widths in multiples of 8), "simple" = token by token; "auto" =
         # grouped from `moe_grouped_min` (token, expert) pairs on
-        # per-head products of a latent attention: up to this many tokens on this library's
-        # kernel, more through the library's batched product
-        self.heads_small_n = int(os.environ.get("RVLLM_HEADS_SMALL_N", "64"))
         self.moe_mode = os.environ.get("RVLLM_MOE", "auto")
         self.moe_grouped_min = int(os.environ.get("RVLLM_MOE_GROUPED_MIN", "16"))
         # float32 products must be float32: no TF32, no reduced-precision accumulation
@@ -918,24 +915,17 @@ class CudaOps:
 
     def heads_product(self, rows, offset, heads, size, w, out, gate_rows=None, gate_off=-1):
         """out[n, h, :] = rows[n, offset + h * size : + size] . w[h] for w [heads, size, b]: one
-        small product per head; with `gate_rows` the result is multiplied by
-        sigmoid(gate_rows[n, gate_off + ...]).  Up to `heads_small_n` tokens: one kernel of this
-        library (float32 sums, the gate in the same pass).  More: one batched library product
-        straight from and into the [tokens, heads * size] layouts (a head is a batch entry
-        whose rows are strided), then the gate kernel."""
+        small product per head, as one batched library product straight from and into the
+        [tokens, heads * size] layouts (a head is a batch entry whose rows are strided); with
+        `gate_rows` the result is then multiplied by sigmoid(gate_rows[n, gate_off + ...]).
+        (A kernel of this library for few tokens, one block per head and eight tokens with
+        the gate in the same pass, measured 10 us a call inside a captured step where the
+        library's product takes 2; it is not kept.)"""
         n = rows.shape[0]
         b = w.shape[2]
         if n == 0:
             return
         self._need(w, "per-head matrices", rows.dtype)
-        if n <= self.heads_small_n and size * 32 <= 48 * 1024:
-            self._check(self.lib.rv_heads_product(
-                _ptr(rows), _code(rows.dtype), c_int(rows.stride(0)), c_int(offset), c_int(n),
-                c_int(heads), c_int(size), c_int(b), _ptr(w), _ptr(out), c_int(out.stride(0)),
-                _ptr(gate_rows), c_int(gate_rows.stride(0) if gate_rows is not None else 0),
-                c_int(gate_off if gate_rows is not None else -1), self._stream()),
-                "heads_product")
-            return
         x = rows.as_strided((heads, n, size), (size, rows.stride(0), 1),
                             rows.storage_offset() + offset)
         y = out.as_strided((heads, n, b), (b, out.stride(0), 1), out.storage_offset())

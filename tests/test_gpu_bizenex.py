@@ -114,7 +114,7 @@ def _case(H, G, d, dv, S, seed, dtype):
 
 
 SIZES = [(6, 2, 32, 16), (4, 4, 16, 48), (3, 1, 24, 8), (8, 2, 64, 64), (16, 2, 128, 128),
-         (3, 3, 10, 6), (6, 1, 96, 96), (5, 1, 40, 40)]
+         (3, 3, 10, 6), (6, 1, 96, 96), (5, 1, 40, 40), (4, 1, 160, 160), (2, 1, 320, 320)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -260,8 +260,8 @@ def test_latent_norm_write(ops, dtype, rank):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_heads_product_and_gate(ops, dtype):
-    """Few tokens (this library's kernel) and many (the batched library product), with the gate
-    in the same call and as a kernel of its own."""
+    """Few tokens and many, sizes that nothing divides, with the gate in the same call and as a
+    kernel of its own."""
     g = torch.Generator().manual_seed(3)
     for n, H, a, b, offset in ((7, 3, 10, 6, 4), (130, 6, 32, 96, 0), (1, 8, 96, 80, 16), (64, 5, 24, 200, 8),
                                (65, 2, 128, 64, 0), (9, 4, 512, 40, 0)):
