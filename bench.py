@@ -875,7 +875,7 @@ def bizenex_config(sz):
             layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
         else:
             mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"],
-                     "scale": 12.0 / sz["dim"] ** 0.5, "q_temp": {"coef": 0.5, "every": 128}}
+                     "scale": 12.0 / sz["dim"] ** 0.5, "q_temp": {"coef": 0.4, "every": 256}}
             layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
     return {"architecture": "Bizenex", "vocab": sz["vocab"], "width": sz["width"],
             "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": layers}

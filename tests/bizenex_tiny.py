@@ -84,7 +84,7 @@ BZ_D = {
     "layers": [
         {"type": "latent_attention", "mixer": _latent(8, 32, 48, 64, 0.18),
          "mlp": _moe(128, 8, 2, (4, 2))},
-        {"type": "attention", "mixer": _attn(8, 2, 64, 64, 0.2, (0.5, 16)),
+        {"type": "attention", "mixer": _attn(12, 3, 64, 64, 0.2, (0.4, 16)),
          "mlp": _moe(64, 16, 4, (4, 3))},
         {"type": "latent_attention", "mixer": _latent(4, 64, 32, 64, 0.12, kv_from=0),
          "mlp": _moe(128, 4, 2)},

@@ -113,8 +113,8 @@ def _case(H, G, d, dv, S, seed, dtype):
     return rnd(S, H, d), rnd(S, G, d), rnd(S, G, dv), rnd(H).float().double()
 
 
-SIZES = [(6, 2, 32, 16), (4, 4, 16, 48), (3, 1, 24, 8), (8, 2, 64, 64), (16, 2, 128, 128),
-         (3, 3, 10, 6), (6, 1, 96, 96), (5, 1, 40, 40), (4, 1, 160, 160), (2, 1, 320, 320)]
+SIZES = [(6, 2, 32, 16), (4, 4, 16, 48), (3, 1, 24, 8), (8, 4, 64, 64), (16, 2, 128, 128),
+         (3, 3, 10, 6), (6, 1, 80, 80), (5, 1, 40, 40), (4, 1, 160, 160), (2, 1, 320, 320)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -137,7 +137,7 @@ def test_attention_with_sinks_against_plain(ops, dtype, sizes):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(8, 2, 64, 64), (6, 1, 96, 96), (4, 4, 32, 32)])
+@pytest.mark.parametrize("sizes", [(8, 4, 64, 64), (5, 1, 112, 112), (4, 4, 32, 32)])
 def test_short_portion_after_a_long_context(ops, dtype, sizes):
     """A few tokens at the end of 1,500: the kernels that share a block's keys out over several
     blocks and merge the parts count the sink once."""
@@ -151,7 +151,7 @@ def test_short_portion_after_a_long_context(ops, dtype, sizes):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(4, 2, 32, 16), (8, 2, 64, 64), (6, 1, 96, 96)])
+@pytest.mark.parametrize("sizes", [(4, 2, 32, 16), (8, 4, 64, 64), (6, 1, 80, 80)])
 def test_attention_one_key_stands_out(ops, dtype, sizes):
     """Among 700 keys one is made to win: the first tokens, far back, on both sides of page
     and split borders, the query's own and the one before.  A kernel that loses that key is
@@ -197,7 +197,7 @@ def test_sink_takes_weight(ops, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(5, 2, 24, 40), (3, 3, 64, 16), (4, 1, 10, 6), (2, 0, 16, 8),
-                                   (6, 2, 64, 64), (3, 1, 8, 8), (5, 5, 256, 256), (7, 0, 32, 32)])
+                                   (6, 3, 64, 64), (3, 1, 8, 8), (5, 5, 256, 256), (7, 0, 32, 32)])
 def test_qk_unit_write(ops, dtype, sizes):
     H, G, d, dv = sizes
     g = torch.Generator().manual_seed(H * 100 + d)
@@ -241,7 +241,7 @@ def test_query_temperature_steps():
 # ---- latent rows, the products per head, the gate -----------------------------------------------
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rank", [14, 32, 96, 520])
+@pytest.mark.parametrize("rank", [14, 32, 88, 520])
 def test_latent_norm_write(ops, dtype, rank):
     g = torch.Generator().manual_seed(rank)
     n, offset = 9, 11
@@ -263,7 +263,7 @@ def test_heads_product_and_gate(ops, dtype):
     """Few tokens and many, sizes that nothing divides, with the gate in the same call and as a
     kernel of its own."""
     g = torch.Generator().manual_seed(3)
-    for n, H, a, b, offset in ((7, 3, 10, 6, 4), (130, 6, 32, 96, 0), (1, 8, 96, 80, 16), (64, 5, 24, 200, 8),
+    for n, H, a, b, offset in ((7, 3, 10, 6, 4), (130, 6, 32, 96, 0), (1, 8, 112, 72, 16), (64, 5, 24, 200, 8),
                                (65, 2, 128, 64, 0), (9, 4, 512, 40, 0)):
         rows = torch.randn(n, offset + H * a + 9, generator=g).to(dtype)
         w = (torch.randn(H, a, b, generator=g) * 0.3).to(dtype)
@@ -283,7 +283,7 @@ def test_heads_product_and_gate(ops, dtype):
 
 # ---- mixture of experts ---------------------------------------------------------------------------
 
-@pytest.mark.parametrize("shape", [(8, 4, 2, 1), (8, 2, 1, 1), (6, 2, 3, 2), (9, 3, 3, 1), (64, 6, 8, 3),
+@pytest.mark.parametrize("shape", [(8, 3, 2, 1), (8, 2, 1, 1), (6, 2, 3, 2), (9, 3, 3, 1), (64, 6, 8, 3),
                                    (4, 1, 1, 1), (5, 5, 1, 1), (12, 3, 12, 4), (256, 8, 8, 4), (40, 33, 1, 1)])
 def test_moe_select(ops, shape):
     E, top, groups, keep = shape
@@ -307,7 +307,7 @@ def test_moe_select(ops, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(50, 5, 2, 5, 3), (96, 8, 4, 2, 1), (1024, 64, 6, 8, 3), (333, 9, 3, 1, 1),
+@pytest.mark.parametrize("shape", [(50, 5, 2, 5, 3), (96, 8, 3, 2, 1), (1024, 64, 6, 8, 3), (333, 9, 3, 1, 1),
                                    (256, 128, 8, 8, 4), (4000, 16, 4, 4, 2)])
 def test_moe_route(ops, dtype, shape):
     """The router's product and the choice in one kernel against the plain route on float64
@@ -329,7 +329,7 @@ def test_moe_route(ops, dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(50, 34, 5, 2), (96, 64, 6, 2), (320, 96, 8, 4), (128, 256, 4, 1),
+@pytest.mark.parametrize("shape", [(50, 34, 5, 2), (96, 64, 6, 2), (336, 104, 10, 5), (128, 256, 4, 1),
                                    (64, 48, 16, 16), (512, 264, 4, 2)])
 @pytest.mark.parametrize("n", [1, 3, 37, 300, 1500])
 def test_moe_experts(ops, dtype, shape, n):
@@ -357,8 +357,8 @@ def test_moe_experts(ops, dtype, shape, n):
 def test_softcap(ops):
     x = torch.randn(5, 1001) * 40
     y = dev(x.clone())
-    ops.softcap(y, 15.0)
-    close(y, 15.0 * torch.tanh(x.double() / 15.0), torch.float32)
+    ops.softcap(y, 12.0)
+    close(y, 12.0 * torch.tanh(x.double() / 12.0), torch.float32)
 
 
 # ---- the engine ---------------------------------------------------------------------------
