@@ -92,8 +92,25 @@ BZ_D = {
     ],
 }
 
-CONFIGS = {"A": BZ_A, "B": BZ_B, "C": BZ_C, "D": BZ_D}
-SEEDS = {"A": 21, "B": 22, "C": 23, "D": 24}
+# larger heads and ranks: a rank beyond the tensor-core kernels' head sizes, key and value heads of
+# 128, many experts of a size that no tile divides, a reader right after its source and one later
+BZ_E = {
+    "architecture": "Bizenex", "vocab": 500, "width": 256, "norm": {"eps": 1e-6},
+    "logit_softcap": 10.0,
+    "layers": [
+        {"type": "attention", "mixer": _attn(4, 4, 128, 128, 0.3, (0.3, 50)),
+         "mlp": _moe(200, 32, 6, (8, 4))},
+        {"type": "latent_attention", "mixer": _latent(8, 64, 64, 192, 0.1),
+         "mlp": _moe(72, 64, 8, (4, 1))},
+        {"type": "latent_attention", "mixer": _latent(3, 32, 96, 192, 0.2, kv_from=1), "mlp": None},
+        {"type": "attention", "mixer": _attn(16, 2, 32, 64, 0.25), "mlp": _moe(200, 32, 6, (8, 4))},
+        {"type": "latent_attention", "mixer": _latent(8, 64, 64, 192, 0.1, kv_from=1),
+         "mlp": _moe(128, 3, 1)},
+    ],
+}
+
+CONFIGS = {"A": BZ_A, "B": BZ_B, "C": BZ_C, "D": BZ_D, "E": BZ_E}
+SEEDS = {"A": 21, "B": 22, "C": 23, "D": 24, "E": 25}
 
 
 def config(name: str) -> dict:

@@ -412,7 +412,7 @@ def _requests(name, lengths, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_every_cut_equals_plain(folders, name, dtype):
     """Whole prompts; a prompt then its last tokens one by one (past several temperature
     steps); portions down to two tokens; mixed batches of unequal requests on four slots,
