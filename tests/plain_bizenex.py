@@ -26,7 +26,7 @@ def rms_unit(x, eps):
 
 
 def sigmoid(z):
-    return 1.0 / (1.0 + np.exp(-z))
+    return 1.0 / (1.0 + np.exp(-np.clip(z, -700.0, 700.0)))
 
 
 def softmax_with_sink(scores, sink):
